@@ -1,0 +1,136 @@
+"""The CPU checker against (1) the committed vectors produced by the reference
+project's own code and (2), where it is built, that code itself."""
+import numpy as np
+import pytest
+
+import oracle
+
+
+def test_fill_random_matches_reference_vectors(golden):
+    assert np.array_equal(oracle.fill_random(96, 42), golden["fill_seed42"])
+    assert np.array_equal(oracle.fill_random(96, 99), golden["fill_seed99"])
+    v = oracle.fill_random(4096, 42)
+    assert v.min() >= -1.0 and v.max() < 1.0
+
+
+def test_sgemm_matches_reference_vectors(golden):
+    a = oracle.fill_random(24 * 40, 42).reshape(24, 40)
+    b = oracle.fill_random(40 * 16, 99).reshape(40, 16)
+    assert np.array_equal(oracle.sgemm(a, b), golden["sgemm_c"])
+
+
+@pytest.mark.parametrize("M,K", [(32, 64), (48, 128)])
+def test_sparse_format_matches_reference_vectors(golden, M, K):
+    dense = oracle.gen_sparse_2_4_ref(M, K, 42)
+    assert np.array_equal(dense, golden[f"sp_dense_{M}x{K}"])       # same libc rand() stream
+    comp, meta = oracle.compress_2_4_ref(dense)
+    assert np.array_equal(comp, golden[f"sp_comp_{M}x{K}"])
+    assert np.array_equal(meta, golden[f"sp_meta_{M}x{K}"])
+    assert meta.size == oracle.sparse_meta_count(M, K) == (M // 16) * (K // 32) * 8
+    # decompression inverts compression
+    assert np.array_equal(oracle.decompress_2_4_ref(comp, meta, M, K), dense)
+    # exact int32 GEMM
+    b = golden[f"sp_b_{M}x{K}"]
+    c = golden[f"sp_c_{M}x{K}"]
+    assert np.array_equal(oracle.igemm(dense, b), c)
+    assert np.array_equal(oracle.igemm(dense, b, threads=3), c)
+    assert np.array_equal(oracle.igemm_mnk(dense, b), c)
+    assert np.array_equal(oracle.igemm_nt(dense, np.ascontiguousarray(b.T)), c)
+    assert np.array_equal(dense.astype(np.int64) @ b.astype(np.int64), c)
+    # per-row nibble format carries the same positions
+    nib = oracle.meta_ref_to_rows(meta, M, K)
+    assert np.array_equal(oracle.decompress_rows(comp, nib), dense)
+
+
+def test_check_fp32_and_logic(golden):
+    r = oracle.check_fp32(golden["check_gpu"], golden["check_ref"], 0.5, 0.1)
+    assert [r["num_errors"], r["first_error"]] == list(golden["check_result"])
+    assert np.allclose([r["max_abs"], r["max_rel"]], golden["check_max"], rtol=0, atol=0)
+    # element 1 (abs 0.6, rel 0.06) passes: both limits must be exceeded to fail
+    assert r["num_errors"] == 2
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference build absent")
+def test_restatement_equals_reference_build_on_fresh_inputs():
+    for seed in (1, 42, 1234):
+        assert np.array_equal(oracle.fill_random(1000, seed), oracle.ref_fill_random(1000, seed))
+        d0 = oracle.gen_sparse_2_4_ref(64, 96, seed)
+        d1 = oracle.ref_gen_random_sparse_2_4_int8(64, 96, seed)
+        assert np.array_equal(d0, d1)
+        c0, m0 = oracle.compress_2_4_ref(d0)
+        c1, m1 = oracle.ref_compress_2_4_int8(d1)
+        assert np.array_equal(c0, c1) and np.array_equal(m0, m1)
+        b = oracle.gen_int8((96, 40), seed, 5)
+        ref_c = oracle.ref_cpu_sparse_gemm_int8(d1, b)
+        assert np.array_equal(oracle.igemm(d0, b), ref_c)
+        assert np.array_equal(oracle.ref_cpu_sparse_gemm_int8(d1, b, threads=4), ref_c)
+    # compressor fall-backs on groups with fewer than two non-zeros (sparse_meta_int8.h:160-161)
+    d = np.zeros((16, 32), np.int8)
+    d[0, 1] = 5
+    d[3, 7] = -9
+    c0, m0 = oracle.compress_2_4_ref(d)
+    c1, m1 = oracle.ref_compress_2_4_int8(d)
+    assert np.array_equal(c0, c1) and np.array_equal(m0, m1)
+    a = oracle.fill_random(20 * 12, 3).reshape(20, 12)
+    bb = oracle.fill_random(12 * 8, 4).reshape(12, 8)
+    assert np.array_equal(oracle.sgemm(a, bb), oracle.ref_cpu_sgemm(a, bb))
+
+
+def test_quantize_symmetric():
+    x = oracle.fill_random(4096, 42)
+    s = oracle.compute_scale(x)
+    assert s == np.float32(np.abs(x).max()) / np.float32(127.0)
+    q = oracle.quantize_symmetric(x, s)
+    assert q.dtype == np.int8 and q.max() == 127 and q.min() >= -128
+    expect = np.clip(np.sign(x * (np.float32(1.0) / np.float32(s))) *
+                     np.floor(np.abs(x * (np.float32(1.0) / np.float32(s))) + np.float32(0.5)), -128, 127)
+    assert np.array_equal(q, expect.astype(np.int8))
+    assert oracle.compute_scale(np.zeros(8, np.float32)) == 1.0
+
+
+def test_epilogues():
+    rng = np.random.default_rng(0)
+    acc = rng.integers(-(2 ** 26), 2 ** 26, size=(8, 12), dtype=np.int32)
+    sa, sb = np.float32(0.013), np.float32(0.0071)
+    got = oracle.dequant_per_tensor(acc, sa, sb)
+    assert np.array_equal(got, acc.astype(np.float32) * (sa * sb))
+    scale, zp = oracle.gen_per_channel_params(12, sa, sb)
+    assert zp.min() >= -2 and zp.max() <= 2
+    got = oracle.dequant_per_channel(acc, scale, zp)
+    assert np.array_equal(got, (acc.astype(np.float32) - zp.astype(np.float32)[None, :]) * scale[None, :])
+    sa_m = oracle.gen_scales(8, 0, 1)
+    sw_n = oracle.gen_scales(12, 0, 2)
+    assert sa_m.min() >= 1e-3 and sa_m.max() <= 2e-2
+    got = oracle.dequant_w8a8_f16(acc, sa_m, sw_n)
+    y = acc.astype(np.float32) * (sa_m[:, None] * sw_n[None, :])
+    assert np.array_equal(got.view(np.uint16), y.astype(np.float16).view(np.uint16))
+
+
+def test_f32_to_f16_round_to_nearest_even():
+    rng = np.random.default_rng(1)
+    bits = rng.integers(0, 2 ** 32, size=20000, dtype=np.uint64).astype(np.uint32)
+    special = np.array([0, 0x80000000, 0x33000000, 0x33000001, 0x387FC000, 0x387FE000, 0x477FEFFF,
+                        0x477FF000, 0x7F800000, 0xFF800000, 0x38800000, 0x3F801000, 0x3F803000], np.uint32)
+    f = np.concatenate([bits, special]).view(np.float32)
+    f = f[~np.isnan(f)]
+    with np.errstate(over="ignore"):
+        want = f.astype(np.float16).view(np.uint16)
+    got = np.array([oracle.lib().orc_f32_to_f16(float(x)) for x in f], np.uint16)
+    assert np.array_equal(got, want)
+
+
+def test_seeded_generators():
+    s = oracle.stream_id("C2", "A")
+    a = oracle.gen_int8((64, 128), 0, s)
+    assert np.array_equal(a, oracle.gen_int8((64, 128), 0, s))
+    assert a.min() >= -127 and a.max() <= 127 and not np.array_equal(a, oracle.gen_int8((64, 128), 1, s))
+    big = oracle.gen_int8((1 << 16,), 0, s).astype(np.int32)
+    assert abs(big.mean()) < 1.5 and len(np.unique(big)) == 255
+    comp, nib = oracle.gen_sparse_rows(32, 256, 0, oracle.stream_id("C3", "W"))
+    assert (comp != 0).all()
+    lo, hi = nib & 0xF, nib >> 4
+    for n in (lo, hi):
+        assert ((n & 3) < (n >> 2)).all()
+    assert len(np.unique(lo)) == 6
+    dense = oracle.decompress_rows(comp, nib)
+    assert ((dense.reshape(32, 64, 4) != 0).sum(axis=2) == 2).all()
