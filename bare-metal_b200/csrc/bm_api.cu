@@ -1,0 +1,394 @@
+// bm_api.cu — the extern "C" launchers declared in include/bm_igemm.h.
+// Argument validation, tensor-map encoding, tile-shape choice and the kernel launch; no
+// arithmetic happens on the host.
+#include <cstdlib>
+
+#include "host_common.cuh"
+#include "igemm_dense.cuh"
+#include "igemm_sparse.cuh"
+#include "pack_kernels.cuh"
+
+namespace bm {
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Testing hook: BM_FORCE_BN=<width> pins the tile width so every instantiation can be
+// exercised on small problems.  Unset (the default) lets the launcher choose.
+static int forced_bn() {
+    const char* e = getenv("BM_FORCE_BN");
+    return e ? atoi(e) : 0;
+}
+
+static int validate_epilogue(int epi, const void* out, long long ld, int cols, const float* row_scale,
+                             const float* col_scale, const int* col_zero) {
+    if (!out) return fail_msg(BM_ERR_NULL, "output pointer is NULL");
+    if (ld < cols) return fail_msg(BM_ERR_SHAPE, "output pitch is smaller than the row length");
+    if (epi == EPI_F32_CHANNEL && (!col_scale || !col_zero)) return fail_msg(BM_ERR_NULL, "scale / zero_point is NULL");
+    if (epi == EPI_F16_ROWCOL && (!row_scale || !col_scale)) return fail_msg(BM_ERR_NULL, "row / column scale is NULL");
+    return BM_OK;
+}
+
+static size_t out_elem_size(int epi) { return epi == EPI_F16_ROWCOL ? 2 : 4; }
+
+// =========================================================================================
+// dense
+// =========================================================================================
+template <int BN, bool B_MN, int EPI>
+static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const DenseParams& p, int grid,
+                             cudaStream_t stream) {
+    using Cfg = DenseCfg<BN>;
+    auto kern = igemm_dense_kernel<BN, B_MN, EPI>;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    BM_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev]) {
+        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured[dev] = true;
+    }
+    kern<<<grid, kDenseThreads, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
+    BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
+}
+
+template <bool B_MN, int EPI>
+static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const DenseParams& p, int grid,
+                           cudaStream_t stream) {
+    switch (bn) {
+        case 256: return launch_dense_inst<256, B_MN, EPI>(ma, mb, p, grid, stream);
+        case 128: return launch_dense_inst<128, B_MN, EPI>(ma, mb, p, grid, stream);
+        case 64:
+            if constexpr (!B_MN) return launch_dense_inst<64, B_MN, EPI>(ma, mb, p, grid, stream);
+        default: return fail_msg(BM_ERR_SHAPE, "unsupported tile width");
+    }
+}
+
+static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M, int N, int K, long long ldc,
+                      int b_layout, float tensor_scale, const float* row_scale, const float* col_scale,
+                      const int* col_zero, void* stream_v) {
+    if (!A || !B) return fail_msg(BM_ERR_NULL, "operand pointer is NULL");
+    if (M <= 0 || N <= 0 || K <= 0) return fail_msg(BM_ERR_SHAPE, "M, N, K must be positive");
+    if (b_layout != BM_B_KN && b_layout != BM_B_NK) return fail_msg(BM_ERR_LAYOUT, "unknown B layout tag");
+    if (K % 16 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a multiple of 16 (16-byte row pitch of A)");
+    if (b_layout == BM_B_KN && N % 16 != 0)
+        return fail_msg(BM_ERR_SHAPE, "N must be a multiple of 16 for B[K x N] (16-byte row pitch of B)");
+    if (!aligned16(A) || !aligned16(B)) return fail_msg(BM_ERR_ALIGN, "operands must be 16-byte aligned");
+    if (int rc = validate_epilogue(epi, C, ldc, N, row_scale, col_scale, col_zero)) return rc;
+
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+
+    const bool b_mn = (b_layout == BM_B_KN);
+    const int tiles_m = ceil_div(M, kBM);
+    int bn = forced_bn();
+    if (bn == 0) {
+        // widest tile that still gives every SM work; narrow tiles for small problems
+        const int min_bn = b_mn ? 128 : 64;
+        bn = min_bn;
+        for (int cand = 256; cand >= min_bn; cand >>= 1)
+            if (tiles_m * ceil_div(N, cand) >= dev->sm_count || cand == min_bn) { bn = cand; break; }
+        if (N <= bn / 2 && bn / 2 >= min_bn) bn /= 2;
+    }
+    if (b_mn && bn < 128) bn = 128;
+
+    CUtensorMap map_a, map_b;
+    if (int rc = make_tensor_map_u8(&map_a, A, K, M, K, kBK, kBM, true)) return rc;
+    if (b_mn) {
+        if (int rc = make_tensor_map_u8(&map_b, B, N, K, N, 128, kBK, true)) return rc;
+    } else {
+        if (int rc = make_tensor_map_u8(&map_b, B, K, N, K, kBK, bn, true)) return rc;
+    }
+
+    DenseParams p{};
+    p.epi.out = C;
+    p.epi.ld = ldc;
+    p.epi.rows = M;
+    p.epi.cols = N;
+    p.epi.tensor_scale = tensor_scale;
+    p.epi.row_scale = row_scale;
+    p.epi.col_scale = col_scale;
+    p.epi.col_zero = col_zero;
+    p.epi.vec_ok = aligned16(C) && (static_cast<size_t>(ldc) * out_elem_size(epi)) % 16 == 0;
+    p.tiles_m = tiles_m;
+    p.tiles_n = ceil_div(N, bn);
+    p.k_blocks = ceil_div(K, kBK);
+    p.status = dev->status;
+    if (const char* e = getenv("BM_DBG_LBO")) p.dbg_lbo = atoi(e);
+    if (const char* e = getenv("BM_DBG_SBO")) p.dbg_sbo = atoi(e);
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int grid = num_tiles < dev->sm_count ? num_tiles : dev->sm_count;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+#define BM_DENSE_CASE(E)                                                                        \
+    case E:                                                                                     \
+        return b_mn ? launch_dense_bn<true, E>(bn, map_a, map_b, p, grid, stream)               \
+                    : launch_dense_bn<false, E>(bn, map_a, map_b, p, grid, stream);
+    switch (epi) {
+        BM_DENSE_CASE(EPI_I32)
+        BM_DENSE_CASE(EPI_F32_TENSOR)
+        BM_DENSE_CASE(EPI_F32_CHANNEL)
+        BM_DENSE_CASE(EPI_F16_ROWCOL)
+    }
+#undef BM_DENSE_CASE
+    return fail_msg(BM_ERR_LAYOUT, "unknown epilogue");
+}
+
+// =========================================================================================
+// sparse
+// =========================================================================================
+static size_t meta_tiled_bytes(int R, int K) {
+    return static_cast<size_t>(ceil_div(R, 128)) * ceil_div(K, kSpKLogical) * kSpMetaBytes;
+}
+
+static int pack_meta(const void* meta_in, int fmt, void* tiled, int R, int K, cudaStream_t stream) {
+    if (!meta_in || !tiled) return fail_msg(BM_ERR_NULL, "metadata pointer is NULL");
+    if (R <= 0 || K <= 0 || K % 32 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 32");
+    if (fmt == BM_META_REF && R % 16 != 0) return fail_msg(BM_ERR_SHAPE, "reference metadata needs rows % 16 == 0");
+    if (!aligned16(tiled) || (reinterpret_cast<uintptr_t>(meta_in) & 3u))
+        return fail_msg(BM_ERR_ALIGN, "metadata buffers are misaligned");
+    const int k_blocks = ceil_div(K, kSpKLogical);
+    const size_t units = meta_tiled_bytes(R, K) / 16;
+    const unsigned blocks = static_cast<unsigned>((units + 255) / 256);
+    if (fmt == BM_META_ROWS)
+        pack_meta_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(meta_in),
+                                                          static_cast<uint8_t*>(tiled), R, K, k_blocks, units);
+    else if (fmt == BM_META_REF)
+        pack_meta_ref_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(meta_in),
+                                                         static_cast<uint8_t*>(tiled), R, K, k_blocks, units);
+    else
+        return fail_msg(BM_ERR_LAYOUT, "unknown metadata format tag");
+    BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
+}
+
+template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI>
+static int launch_sparse_inst(const CUtensorMap& ms, const CUtensorMap& md, const SparseParams& p, int grid,
+                              cudaStream_t stream) {
+    using Cfg = SparseCfg<BN>;
+    auto kern = igemm_sparse_kernel<BN, DENSE_MN, TRANSPOSED, EPI>;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    BM_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev]) {
+        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured[dev] = true;
+    }
+    kern<<<grid, kSpThreads, Cfg::SMEM_BYTES, stream>>>(ms, md, p);
+    BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
+}
+
+// mode 0: sparse operand on the left, out[r][c];  mode 1: sparse weights, out[c][r]
+static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* meta_tiled, const int8_t* Dn,
+                       void* out, int R, int Cn, int K, long long ld, int dense_layout, float tensor_scale,
+                       const float* row_scale, const float* col_scale, void* stream_v) {
+    if (!S_comp || !meta_tiled || !Dn) return fail_msg(BM_ERR_NULL, "operand pointer is NULL");
+    if (R <= 0 || Cn <= 0 || K <= 0) return fail_msg(BM_ERR_SHAPE, "dimensions must be positive");
+    if (K % 32 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a multiple of 32 for the 2:4 format");
+    const bool dense_mn = (dense_layout == BM_B_KN);
+    if (dense_mn && Cn % 16 != 0) return fail_msg(BM_ERR_SHAPE, "N must be a multiple of 16 for B[K x N]");
+    if (!aligned16(S_comp) || !aligned16(Dn) || !aligned16(meta_tiled))
+        return fail_msg(BM_ERR_ALIGN, "operands must be 16-byte aligned");
+    const int out_rows = mode == 0 ? R : Cn, out_cols = mode == 0 ? Cn : R;
+    if (int rc = validate_epilogue(epi, out, ld, out_cols, row_scale, col_scale, nullptr)) return rc;
+
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+
+    const int tiles_r = ceil_div(R, kBM);
+    int bn = forced_bn();
+    if (bn == 0) {
+        if (mode == 1) {
+            // tokens on the accumulator columns: the narrowest tile that holds them, up to 128
+            bn = 16;
+            while (bn < 128 && bn < Cn) bn <<= 1;
+            if (Cn > 128 && tiles_r * ceil_div(Cn, 256) >= dev->sm_count) bn = 256;
+        } else {
+            const int min_bn = dense_mn ? 128 : 64;
+            bn = min_bn;
+            for (int cand = 256; cand >= min_bn; cand >>= 1)
+                if (tiles_r * ceil_div(Cn, cand) >= dev->sm_count || cand == min_bn) { bn = cand; break; }
+        }
+    }
+    if (dense_mn && bn < 128) bn = 128;
+    if (mode == 0 && bn < 64) bn = 64;
+
+    CUtensorMap map_s, map_d;
+    if (int rc = make_tensor_map_u8(&map_s, S_comp, K / 2, R, K / 2, 128, kBM, true)) return rc;
+    if (dense_mn) {
+        if (int rc = make_tensor_map_u8(&map_d, Dn, Cn, K, Cn, 128, kSpKLogical, true)) return rc;
+    } else {
+        if (int rc = make_tensor_map_u8(&map_d, Dn, K, Cn, K, 128, bn, true)) return rc;
+    }
+
+    SparseParams p{};
+    p.epi.out = out;
+    p.epi.ld = ld;
+    p.epi.rows = out_rows;
+    p.epi.cols = out_cols;
+    p.epi.tensor_scale = tensor_scale;
+    p.epi.row_scale = row_scale;
+    p.epi.col_scale = col_scale;
+    p.epi.col_zero = nullptr;
+    p.epi.vec_ok = aligned16(out) && (static_cast<size_t>(ld) * out_elem_size(epi)) % 16 == 0;
+    p.meta_tiled = meta_tiled;
+    p.tiles_r = tiles_r;
+    p.tiles_c = ceil_div(Cn, bn);
+    p.k_blocks = ceil_div(K, kSpKLogical);
+    p.status = dev->status;
+    const int num_tiles = p.tiles_r * p.tiles_c;
+    const int grid = num_tiles < dev->sm_count ? num_tiles : dev->sm_count;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+#define BM_SP(BNV, MN, TR, E) return launch_sparse_inst<BNV, MN, TR, E>(map_s, map_d, p, grid, stream)
+    if (mode == 0) {
+        if (epi == EPI_I32) {
+            if (dense_mn) { if (bn == 256) BM_SP(256, true, false, EPI_I32); if (bn == 128) BM_SP(128, true, false, EPI_I32); }
+            else { if (bn == 256) BM_SP(256, false, false, EPI_I32); if (bn == 128) BM_SP(128, false, false, EPI_I32);
+                   if (bn == 64) BM_SP(64, false, false, EPI_I32); }
+        } else if (epi == EPI_F32_TENSOR) {
+            if (dense_mn) { if (bn == 256) BM_SP(256, true, false, EPI_F32_TENSOR); if (bn == 128) BM_SP(128, true, false, EPI_F32_TENSOR); }
+            else { if (bn == 256) BM_SP(256, false, false, EPI_F32_TENSOR); if (bn == 128) BM_SP(128, false, false, EPI_F32_TENSOR);
+                   if (bn == 64) BM_SP(64, false, false, EPI_F32_TENSOR); }
+        }
+    } else if (!dense_mn) {
+        if (epi == EPI_I32) {
+            if (bn == 256) BM_SP(256, false, true, EPI_I32); if (bn == 128) BM_SP(128, false, true, EPI_I32);
+            if (bn == 64) BM_SP(64, false, true, EPI_I32);   if (bn == 32) BM_SP(32, false, true, EPI_I32);
+            if (bn == 16) BM_SP(16, false, true, EPI_I32);
+        } else if (epi == EPI_F16_ROWCOL) {
+            if (bn == 256) BM_SP(256, false, true, EPI_F16_ROWCOL); if (bn == 128) BM_SP(128, false, true, EPI_F16_ROWCOL);
+            if (bn == 64) BM_SP(64, false, true, EPI_F16_ROWCOL);   if (bn == 32) BM_SP(32, false, true, EPI_F16_ROWCOL);
+            if (bn == 16) BM_SP(16, false, true, EPI_F16_ROWCOL);
+        }
+    }
+#undef BM_SP
+    return fail_msg(BM_ERR_SHAPE, "unsupported sparse GEMM configuration");
+}
+
+}  // namespace bm
+
+// =========================================================================================
+// C ABI
+// =========================================================================================
+using namespace bm;
+
+extern "C" {
+
+int bm_igemm_i8_i32(const int8_t* A, const int8_t* B, int32_t* C, int M, int N, int K, int64_t ldc, int b_layout,
+                    void* stream) {
+    return dense_gemm(EPI_I32, A, B, C, M, N, K, ldc, b_layout, 1.f, nullptr, nullptr, nullptr, stream);
+}
+
+int bm_igemm_i8_f32(const int8_t* A, const int8_t* B, float* C, int M, int N, int K, float scale_a, float scale_b,
+                    int64_t ldc, int b_layout, void* stream) {
+    // the reference multiplies the two scales first (igemm.cu:104), in fp32
+    volatile float dequant = scale_a * scale_b;
+    return dense_gemm(EPI_F32_TENSOR, A, B, C, M, N, K, ldc, b_layout, dequant, nullptr, nullptr, nullptr, stream);
+}
+
+int bm_igemm_i8_f32_perchannel(const int8_t* A, const int8_t* B, float* C, int M, int N, int K, const float* scale_n,
+                               const int32_t* zero_point_n, int64_t ldc, int b_layout, void* stream) {
+    return dense_gemm(EPI_F32_CHANNEL, A, B, C, M, N, K, ldc, b_layout, 1.f, nullptr, scale_n, zero_point_n, stream);
+}
+
+int bm_w8a8_f16(const int8_t* X, const int8_t* W, uint16_t* D, const float* sa_m, const float* sw_n, int M, int N,
+                int K, int64_t ldd, int w_layout, void* stream) {
+    return dense_gemm(EPI_F16_ROWCOL, X, W, D, M, N, K, ldd, w_layout, 1.f, sa_m, sw_n, nullptr, stream);
+}
+
+int bm_pack_b_kn_to_nk(const int8_t* B_kn, int8_t* W_nk, int K, int N, void* stream) {
+    if (!B_kn || !W_nk) return fail_msg(BM_ERR_NULL, "pointer is NULL");
+    if (K <= 0 || N <= 0) return fail_msg(BM_ERR_SHAPE, "K and N must be positive");
+    dim3 grid((N + 63) / 64, (K + 63) / 64), block(64, 8);
+    transpose_kn_to_nk_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(B_kn, W_nk, K, N);
+    BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
+}
+
+size_t bm_sp_meta_tiled_bytes(int R, int K) {
+    if (R <= 0 || K <= 0) return 0;
+    return meta_tiled_bytes(R, K);
+}
+
+int bm_sp_pack_meta(const void* meta_in, int meta_format, void* meta_tiled, int R, int K, void* stream) {
+    return pack_meta(meta_in, meta_format, meta_tiled, R, K, static_cast<cudaStream_t>(stream));
+}
+
+// metadata in a caller format is re-tiled into library scratch first (same stream, so ordered)
+static int resolve_meta(const void* meta, int fmt, int R, int K, void* stream, const uint8_t** tiled) {
+    if (fmt == BM_META_TILED) {
+        *tiled = static_cast<const uint8_t*>(meta);
+        return BM_OK;
+    }
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    if (int rc = ensure_scratch(dev, meta_tiled_bytes(R, K))) return rc;
+    if (int rc = pack_meta(meta, fmt, dev->scratch, R, K, static_cast<cudaStream_t>(stream))) return rc;
+    *tiled = static_cast<const uint8_t*>(dev->scratch);
+    return BM_OK;
+}
+
+int bm_igemm_sparse_f32(const int8_t* A_comp, const int8_t* B, float* C, const uint32_t* meta, int M, int N, int K,
+                        float scale_a, float scale_b, void* stream) {
+    if (!meta) return fail_msg(BM_ERR_NULL, "metadata pointer is NULL");
+    if (M <= 0 || M % 16 != 0) return fail_msg(BM_ERR_SHAPE, "M must be a positive multiple of 16");
+    if (K <= 0 || K % 32 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 32");
+    const uint8_t* tiled = nullptr;
+    if (int rc = resolve_meta(meta, BM_META_REF, M, K, stream, &tiled)) return rc;
+    volatile float dequant = scale_a * scale_b;       // igemm_sparse_tiled.cu:365
+    return sparse_gemm(0, EPI_F32_TENSOR, A_comp, tiled, B, C, M, N, K, N, BM_B_KN, dequant, nullptr, nullptr, stream);
+}
+
+int bm_igemm_sparse_i32(const int8_t* A_comp, const void* meta, int meta_format, const int8_t* B, int32_t* C, int M,
+                        int N, int K, int64_t ldc, int b_layout, void* stream) {
+    if (!meta) return fail_msg(BM_ERR_NULL, "metadata pointer is NULL");
+    if (M <= 0 || K <= 0 || K % 32 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 32");
+    if (b_layout != BM_B_KN && b_layout != BM_B_NK) return fail_msg(BM_ERR_LAYOUT, "unknown B layout tag");
+    const uint8_t* tiled = nullptr;
+    if (int rc = resolve_meta(meta, meta_format, M, K, stream, &tiled)) return rc;
+    return sparse_gemm(0, EPI_I32, A_comp, tiled, B, C, M, N, K, ldc, b_layout, 1.f, nullptr, nullptr, stream);
+}
+
+int bm_w8a8_sparse_i32(const int8_t* X, const int8_t* W_comp, const void* W_meta_tiled, int32_t* C, int M, int N, int K,
+                       int64_t ldc, void* stream) {
+    return sparse_gemm(1, EPI_I32, W_comp, static_cast<const uint8_t*>(W_meta_tiled), X, C, N, M, K, ldc, BM_B_NK, 1.f,
+                       nullptr, nullptr, stream);
+}
+
+int bm_w8a8_sparse_f16(const int8_t* X, const int8_t* W_comp, const void* W_meta_tiled, uint16_t* D, const float* sa_m,
+                       const float* sw_n, int M, int N, int K, int64_t ldd, void* stream) {
+    return sparse_gemm(1, EPI_F16_ROWCOL, W_comp, static_cast<const uint8_t*>(W_meta_tiled), X, D, N, M, K, ldd,
+                       BM_B_NK, 1.f, sa_m, sw_n, stream);
+}
+
+int bm_last_device_status(int* code) {
+    if (!code) return fail_msg(BM_ERR_NULL, "code pointer is NULL");
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    BM_CUDA_TRY(cudaDeviceSynchronize());
+    BM_CUDA_TRY(cudaMemcpy(code, dev->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*code != 0) BM_CUDA_TRY(cudaMemset(dev->status, 0, sizeof(int)));
+    return BM_OK;
+}
+
+const char* bm_last_error_string(void) { return error_buffer(); }
+
+void bm_shutdown(void) {
+    std::lock_guard<std::mutex> lock(state_mutex());
+    for (int d = 0; d < kMaxDevices; ++d) {
+        DeviceState& s = device_states()[d];
+        if (!s.ready) continue;
+        int prev = 0;
+        if (cudaGetDevice(&prev) != cudaSuccess) continue;
+        if (cudaSetDevice(d) == cudaSuccess) {
+            cudaFree(s.status);
+            cudaFree(s.scratch);
+        }
+        cudaSetDevice(prev);
+        s = DeviceState{};
+    }
+}
+
+const char* bm_version(void) { return "0.1"; }
+
+}  // extern "C"

@@ -1,0 +1,264 @@
+// igemm_sparse.cuh — 2:4 structured-sparse INT8 GEMM for sm_100a on tcgen05.mma.sp.kind::i8.
+//
+// The sparse operand S [R x K] (stored as its kept half, comp [R x K/2], plus 4-bit-per-group
+// position metadata) always sits in the tensor core's A slot, so its rows are the 128
+// tensor-memory lanes of a tile.  The dense operand takes the B slot, either
+//   DENSE_MN=0  X[C x K] row-major (K-major): rows are the tile's BN accumulator columns
+//   DENSE_MN=1  B[K x C] row-major (the reference ABI, igemm_sparse_tiled.cu:88-96), described
+//               to the MMA as MN-major
+// Output orientation
+//   TRANSPOSED=0  out[r][c]  — sparse operand on the left (reference sparse kernels)
+//   TRANSPOSED=1  out[c][r]  — sparse WEIGHTS W[N x K]: lanes are output channels, accumulator
+//                              columns are tokens (D^T = W * X^T), decode shapes use a narrow BN
+//
+// Per k-block (256 logical K) a stage holds: comp tile 128 x 128 B (128B swizzle, TMA),
+// dense tile BN x 256 B (two 128B-swizzled boxes) and 4 KiB of metadata (one bulk copy).
+// The MMA lane copies the metadata shared -> tensor memory with two tcgen05.cp.128x128b
+// (each: 128 rows x 16 B = 128 logical K) and issues four tcgen05.mma.sp (K = 64 logical);
+// each reads its 2 metadata columns.  Metadata has its own tensor-memory columns per stage.
+//
+// Metadata, tiled order (what bm_sp_pack_meta writes): for row block rb (128 rows) and
+// k-block kb (256 logical K): 2 chunks x 128 rows x 16 bytes, chunk-major; byte b of a
+// row's 16 covers logical K [8b, 8b+8): low nibble = first group of 4, high nibble = second;
+// nibble = (idx1 << 2) | idx0.
+//
+// HBM traffic per launch (algorithmic): R*K/2 + R*K/8 + C*K bytes in, R*C*sizeof(out) out.
+#pragma once
+#include "epilogue.cuh"
+#include "igemm_dense.cuh"
+#include "sm100_ptx.cuh"
+
+namespace bm {
+
+constexpr int kSpKLogical = 256;                 // logical K per stage
+constexpr int kSpMetaBytes = 4096;               // metadata bytes per (128-row block, k-block)
+constexpr int kSpThreads = 192;
+constexpr int kSpSmemBudget = 216 * 1024;
+
+template <int BN>
+struct SparseCfg {
+    static constexpr int A_BYTES = kBM * 128;                     // 16 KiB compressed
+    static constexpr int B_BYTES = BN * kSpKLogical;              // dense operand
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + kSpMetaBytes;
+    static constexpr int STAGES_RAW = kSpSmemBudget / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int E_COLS = STAGES * 8;                     // 2 x tcgen05.cp of 4 columns per stage
+    static constexpr int ACC_BUFS = (2 * BN + E_COLS <= 512) ? 2 : 1;
+    static constexpr int E_BASE = ACC_BUFS * BN;
+    static constexpr int COLS_NEEDED = E_BASE + E_COLS;
+    static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
+                                   : COLS_NEEDED <= 256 ? 256 : 512;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16 + 1024;
+    static_assert(STAGES >= 2, "tile too large for the shared-memory ring");
+    static_assert(COLS_NEEDED <= 512, "tensor memory over-subscribed");
+};
+
+struct SparseParams {
+    EpilogueParams epi;
+    const uint8_t* meta_tiled;
+    int tiles_r, tiles_c, k_blocks;    // row blocks of the sparse operand, column tiles of the dense one
+    int* status;
+};
+
+template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI>
+__global__ void __launch_bounds__(kSpThreads, 1)
+igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_d,
+                    const SparseParams p) {
+    using Cfg = SparseCfg<BN>;
+    static_assert(!DENSE_MN || BN % 128 == 0, "MN-major dense operand is loaded in 128-column boxes");
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t a_smem0 = smem_base;
+    const uint32_t b_smem0 = a_smem0 + Cfg::STAGES * Cfg::A_BYTES;
+    const uint32_t e_smem0 = b_smem0 + Cfg::STAGES * Cfg::B_BYTES;
+    const uint32_t bar0 = smem_base + Cfg::BAR_OFFSET;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (Cfg::STAGES + s); };
+    auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * Cfg::STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * Cfg::STAGES + 2 + a); };
+    const uint32_t drain_bar = bar0 + 8u * (2 * Cfg::STAGES + 4);
+    const uint32_t tmem_slot = bar0 + 8u * (2 * Cfg::STAGES + 5);
+    volatile uint32_t* tmem_slot_gen =
+        reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::BAR_OFFSET + 8 * (2 * Cfg::STAGES + 5));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot_gen + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_r * p.tiles_c;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 4);
+        }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            prefetch_tensormap(&map_s);
+            prefetch_tensormap(&map_d);
+            uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const int rb = tile % p.tiles_r;
+                const int r0 = rb * kBM;
+                const int c0 = (tile / p.tiles_r) * BN;
+                const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) * p.k_blocks * kSpMetaBytes;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                      DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
+                    const uint32_t bar = full_bar(stage);
+                    mbar_expect_tx(bar, Cfg::STAGE_BYTES);
+                    tma_load_2d(a_smem0 + stage * Cfg::A_BYTES, &map_s, bar, kb * 128, r0);
+                    const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
+                    if constexpr (DENSE_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 128; ++j)   // [256 K rows x 128 C bytes] per box
+                            tma_load_2d(b_addr + j * (128 * kSpKLogical), &map_d, bar, c0 + j * 128,
+                                        kb * kSpKLogical);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)          // [BN rows x 128 K bytes] per box
+                            tma_load_2d(b_addr + j * (BN * 128), &map_d, bar, kb * kSpKLogical + j * 128, c0);
+                    }
+                    bulk_load(e_smem0 + stage * kSpMetaBytes, meta_row + static_cast<size_t>(kb) * kSpMetaBytes,
+                              kSpMetaBytes, bar);
+                    issued |= 1u << stage;
+                    issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                for (int s = 0; s < Cfg::STAGES; ++s)
+                    if (issued & (1u << s)) {
+                        uint64_t t0 = global_timer_ns();
+                        while (!mbar_try_wait(full_bar(s), (issued_parity >> s) & 1u) &&
+                               global_timer_ns() - t0 < 20000000ull) {}
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_i8(kBM, BN, DENSE_MN, true);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
+                                  DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = a_smem0 + stage * Cfg::A_BYTES;
+                    const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
+                    const uint32_t e_addr = e_smem0 + stage * kSpMetaBytes;
+                    const uint32_t e_tmem = tmem_base + Cfg::E_BASE + stage * 8;
+                    // metadata: rows are 16 B apart, 8-row groups 128 B apart, no swizzle
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        tmem_cp_128x128b(e_tmem + 4 * j, make_smem_desc(e_addr + j * 2048, 0, 128, SWIZZLE_NONE_DESC));
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t a_desc = make_smem_desc(a_addr + ks * 32, 0, 1024, SWIZZLE_128B_DESC);
+                        uint64_t b_desc;
+                        if constexpr (DENSE_MN) {
+                            b_desc = make_smem_desc(b_addr + ks * (64 * 128), 128 * kSpKLogical, 1024,
+                                                    SWIZZLE_128B_DESC);
+                        } else {
+                            b_desc = make_smem_desc(b_addr + (ks >> 1) * (BN * 128) + (ks & 1) * 64, 0, 1024,
+                                                    SWIZZLE_128B_DESC);
+                        }
+                        mma_i8_sp(d_tmem, a_desc, b_desc, e_tmem + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(stage));
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(acc_full_bar(acc));
+                if (++acc == Cfg::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (!ok) {
+                tc_commit(drain_bar);
+                uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < 20000000ull) {}
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            const int r0 = (tile % p.tiles_r) * kBM;
+            const int c0 = (tile / p.tiles_r) * BN;
+            if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
+                break;
+            tc_fence_after_sync();
+            const int lane_coord = r0 + quarter * 32 + lane;      // row of the sparse operand
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            const int c_limit = TRANSPOSED ? p.epi.rows : p.epi.cols;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32 || (BN < 32 && c == 0); ++c) {
+                if (c0 + c * 32 >= c_limit) break;
+                uint32_t r[32];
+                if constexpr (BN >= 32) {
+                    tmem_ld_32x32(taddr + c * 32, r);
+                } else {
+                    // BN = 16: two 8-column loads, the rest of the chunk is masked off below
+                    uint32_t lo[8], hi[8];
+                    tmem_ld_32x8(taddr, lo);
+                    tmem_ld_32x8(taddr + 8, hi);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { r[j] = lo[j]; r[8 + j] = hi[j]; }
+#pragma unroll
+                    for (int j = 16; j < 32; ++j) r[j] = 0;
+                }
+                tmem_ld_wait();
+                if constexpr (TRANSPOSED) {
+                    EpilogueParams e = p.epi;
+                    if (BN < 32 && e.rows > c0 + BN) e.rows = c0 + BN;   // never write past this tile's tokens
+                    store_col_chunk<EPI>(e, lane_coord, c0 + c * 32, r);
+                } else {
+                    store_row_chunk<EPI>(p.epi, lane_coord, c0 + c * 32, r);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if (++acc == Cfg::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+}  // namespace bm

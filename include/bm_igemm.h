@@ -1,0 +1,136 @@
+/*
+ * bm_igemm.h — C ABI of the B200-native INT8 GEMM hot path (libbm_igemm.so).
+ *
+ * This is the drop-in boundary for the quantized-GEMM kernels of pjt222/bare-metal
+ * (kernels/gemm/igemm/).  The reference exposes each kernel as an `extern "C" __global__`
+ * symbol that a C++ host program loads with cuModuleGetFunction and launches with
+ * cuLaunchKernel (kernels/gemm/igemm/bench.cu:85-92,375-378).  Every launcher below takes the
+ * SAME operand pointers, dimensions and scale arguments as the kernel symbol it replaces, in
+ * the same order and with the same meaning, and adds only a trailing layout tag / stream.
+ * Launch geometry, shared memory and tensor maps are the library's business.
+ *
+ * Conventions
+ *   - all matrix pointers are DEVICE pointers owned by the caller; the library never frees
+ *     or reallocates them.  Operand base addresses must be 16-byte aligned.
+ *   - launches are asynchronous on `stream` (a cudaStream_t / CUstream passed as void*;
+ *     NULL = the legacy default stream, as the reference benches use).
+ *   - return value: 0 = launched; negative = argument rejected, nothing was launched
+ *     (the reference kernels have no error channel and silently skip edge tiles,
+ *     igemm_tiled.cu:98-99,162 — here every element of C is written and bad arguments are
+ *     reported); the kernels never abort the process (the reference's CHECK_CU does,
+ *     kernels/_common/bench.h:21-31).
+ *   - plain C types only; no CUDA or torch headers are needed to bind this file.
+ */
+#ifndef BM_IGEMM_H
+#define BM_IGEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------- */
+#define BM_OK                 0
+#define BM_ERR_NULL          (-1)  /* a required pointer is NULL                          */
+#define BM_ERR_SHAPE         (-2)  /* non-positive or unsupported M / N / K               */
+#define BM_ERR_ALIGN         (-3)  /* pointer or leading dimension not 16-byte aligned    */
+#define BM_ERR_LAYOUT        (-4)  /* unknown layout / format tag                         */
+#define BM_ERR_CUDA          (-5)  /* a CUDA call failed; see bm_last_error_string()      */
+#define BM_ERR_TOO_LARGE     (-6)  /* exceeds a documented capacity                       */
+
+/* ---- layout of the right-hand operand (weights) ------------------------------------- */
+#define BM_B_KN 0   /* B[K x N] row-major, N contiguous — the reference ABI (igemm.cu:54)  */
+#define BM_B_NK 1   /* W[N x K] row-major, K contiguous — pre-packed weights               */
+
+/* =======================================================================================
+ * Dense INT8 GEMM, int32 accumulate.  A[M x K] int8 row-major.
+ * Constraints: K % 16 == 0; with BM_B_KN also N % 16 == 0 (16-byte row pitch for TMA).
+ * `ldc` is the row pitch of C in ELEMENTS (>= N), so a rank can write its column slab of a
+ * wider output in place; pass N for a dense C.
+ * ===================================================================================== */
+
+/* Raw accumulators: C[m][n] = sum_k A[m][k] * B[k][n] (int32).  The integer core of every
+ * reference kernel (igemm.cu:52-117); the reference never stores it, the B200 workloads do. */
+int bm_igemm_i8_i32(const int8_t *A, const int8_t *B, int32_t *C, int M, int N, int K,
+                    int64_t ldc, int b_layout, void *stream);
+
+/* Replaces igemm_wmma / igemm_tiled / igemm_register_blocked / igemm_pipelined /
+ * igemm_pipelined_cpasync(_bk64) / igemm_8warp(_256,_256x256,_tribuf) / igemm_persistent
+ * (igemm.cu:52-59 and same-signature siblings; igemm_persistent.cu:60-69 minus its tile
+ * counter): C[m][n] = (float)acc * (scale_a * scale_b). */
+int bm_igemm_i8_f32(const int8_t *A, const int8_t *B, float *C, int M, int N, int K,
+                    float scale_a, float scale_b, int64_t ldc, int b_layout, void *stream);
+
+/* Replaces igemm_pipelined_cpasync_perchannel (igemm_pipelined_cpasync_perchannel.cu:48-56):
+ * C[m][n] = ((float)acc - (float)zero_point[n]) * scale[n]. */
+int bm_igemm_i8_f32_perchannel(const int8_t *A, const int8_t *B, float *C, int M, int N, int K,
+                               const float *scale_n, const int32_t *zero_point_n,
+                               int64_t ldc, int b_layout, void *stream);
+
+/* W8A8 linear of the B200 workloads (no reference counterpart; same integer core):
+ * D[m][n] = half_rn((float)acc * (sa[m] * sw[n])), D is IEEE binary16 (uint16_t bits). */
+int bm_w8a8_f16(const int8_t *X, const int8_t *W, uint16_t *D, const float *sa_m, const float *sw_n,
+                int M, int N, int K, int64_t ldd, int w_layout, void *stream);
+
+/* One-time weight repack B[K x N] -> W[N x K] (excluded from GEMM timing). */
+int bm_pack_b_kn_to_nk(const int8_t *B_kn, int8_t *W_nk, int K, int N, void *stream);
+
+/* =======================================================================================
+ * 2:4 structured-sparse INT8 GEMM.
+ *
+ * The sparse operand S has R rows and logical depth K; it is stored as
+ *   comp [R x K/2] int8 row-major : the two kept values of every aligned group of 4,
+ *                                   lower position first (sparse_meta_int8.h:141-164);
+ *   meta                          : the 2-bit positions, 4 bits per group (idx1 << 2) | idx0,
+ *                                   in one of the formats below.
+ * Constraints: R % 16 == 0 for the reference format; K % 32 == 0.
+ * ===================================================================================== */
+#define BM_META_REF   0  /* uint32 words [(R/16)(K/32)8], rows r and r+8 of a 16-row tile share
+                            one word (sparse_meta_int8.h:13-31,166-175)                      */
+#define BM_META_ROWS  1  /* bytes [R x K/8]: per row, byte j = groups 2j (low nibble), 2j+1  */
+#define BM_META_TILED 2  /* the kernel's own order, produced by bm_sp_pack_meta             */
+
+/* bytes of a BM_META_TILED buffer for an R x K sparse operand */
+size_t bm_sp_meta_tiled_bytes(int R, int K);
+
+/* one-time metadata repack (device -> device) into the kernel's tiled order */
+int bm_sp_pack_meta(const void *meta_in, int meta_format, void *meta_tiled, int R, int K, void *stream);
+
+/* Replaces igemm_sparse_tiled (igemm_sparse_tiled.cu:88-96; also the _ldsm, _ldsm_fused and
+ * _persistent variants minus the tile counter): sparse operand on the LEFT,
+ * C[M x N] = (float)(A_sparse[M x K] * B[K x N]) * (scale_a * scale_b), metadata in the
+ * reference format.  The metadata is re-tiled into library-owned scratch on every call. */
+int bm_igemm_sparse_f32(const int8_t *A_comp, const int8_t *B, float *C, const uint32_t *meta,
+                        int M, int N, int K, float scale_a, float scale_b, void *stream);
+
+/* Sparse-left, int32 out, any metadata format, either layout of the dense operand. */
+int bm_igemm_sparse_i32(const int8_t *A_comp, const void *meta, int meta_format, const int8_t *B,
+                        int32_t *C, int M, int N, int K, int64_t ldc, int b_layout, void *stream);
+
+/* Sparse WEIGHTS (the B200 workloads): W_sparse[N x K] compressed along K, X[M x K] dense.
+ * C[m][n] = sum_k X[m][k] * W[n][k].  Metadata must be BM_META_TILED. */
+int bm_w8a8_sparse_i32(const int8_t *X, const int8_t *W_comp, const void *W_meta_tiled, int32_t *C,
+                       int M, int N, int K, int64_t ldc, void *stream);
+int bm_w8a8_sparse_f16(const int8_t *X, const int8_t *W_comp, const void *W_meta_tiled, uint16_t *D,
+                       const float *sa_m, const float *sw_n, int M, int N, int K, int64_t ldd,
+                       void *stream);
+
+/* =======================================================================================
+ * Library state
+ * ===================================================================================== */
+/* Reads (and clears) the device status word that a bounded in-kernel wait sets when it gives
+ * up: *code 0 = none.  Synchronises the device. */
+int bm_last_device_status(int *code);
+/* Text of the last host-side CUDA error seen by a launcher on this thread. */
+const char *bm_last_error_string(void);
+/* Frees library-owned scratch (metadata staging, status word). */
+void bm_shutdown(void);
+/* "major.minor" of this ABI. */
+const char *bm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BM_IGEMM_H */
