@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""Benchmark of the B200-native INT8 GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 2): W8A8 GEMM M=N=K=4096, int8 operands uniform on [-127,127],
+per-row activation scale and per-column weight scale ~ U[1e-3, 2e-2], fp16 output
+D = half_rn(float(A.W^T) * sa[m]*sw[n]), int32 accumulate.  A "step" is one such GEMM.
+With N > 1 the weight columns are split: every rank owns a 4096-column slab (global
+N = 4096*N, weak scaling), computes its slab and the fp16 outputs are all-gathered.
+
+Prints ONE JSON line (rank 0).  `value` is dense-equivalent TOPS with operands resident in
+HBM; `e2e` is the same metric through the C ABI with HOST buffers (H2D of both operands and
+the scales, D2H of the result, inside the timed region).  `--impl reference` times the
+reference project's own CPU verification GEMM (cpu_sparse_gemm_int8, compiled in place into
+oracle/_ref) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N_LOCAL = K = 4096
+METRIC = "INT8 dense-equiv TOPS at 4096^3 (W8A8 dense, fp16 out)"
+UNIT = "TOPS"
+NOMINAL_INT8_TOPS = 4500.0          # B200 dense INT8 datasheet figure
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [l.split(", ") for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15]
+        if not rows:
+            rows = [l.split(", ") for (_, l) in self.lines]
+        clocks, reasons, smax, power = [], set(), None, []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 7:
+                continue
+            try:
+                clocks.append(float(r[0])); smax = float(r[1]); power.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.strip().lower() == "active":
+                    reasons.add(n)
+        clocks.sort()
+        med = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(clocks),
+                "power_w_max": max(power) if power else None}
+
+
+def reference_arm(args, rank: int, world: int) -> None:
+    """The reference's own CPU verification GEMM on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    import numpy as np
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    cores = os.cpu_count() or 1
+    A = oracle.gen_int8((M, K), 0, oracle.stream_id("C2", "A"))
+    B = oracle.gen_int8((K, N_LOCAL), 0, oracle.stream_id("C2", "Wt"))
+
+    def gemm(rows):
+        a = np.ascontiguousarray(A[:rows])
+        if kind == "reference":
+            return oracle.ref_cpu_sparse_gemm_int8(a, B, threads=cores)
+        return oracle.igemm(a, B, threads=cores)
+
+    probe_rows = min(M, 8 * cores)
+    t = time.perf_counter(); gemm(probe_rows); per_row = (time.perf_counter() - t) / probe_rows
+    rows = int(max(cores, min(M, 0.5 / max(per_row, 1e-9))))      # ~0.5 s per step
+    for _ in range(args.warmup):
+        gemm(rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        gemm(rows)
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = 2.0 * rows * N_LOCAL * K / dt / 1e12
+    sample = f"{rows} of {M} rows of the 4096^3 integer GEMM per step, {cores} host threads on row slabs"
+    line = {"impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "s8*s8->s32", "data": "synthetic",
+            "config": {"workload": "C2 W8A8 GEMM M=N=K=4096 (integer core on CPU)", "sample": sample},
+            "cpu_baseline": {"value": tops, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_leg():
+    import numpy as np
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    cores = os.cpu_count() or 1
+    A = oracle.gen_int8((M, K), 0, oracle.stream_id("C2", "A"))
+    B = oracle.gen_int8((K, N_LOCAL), 0, oracle.stream_id("C2", "Wt"))
+    rows = min(M, max(cores * 8, 1024))
+    a = np.ascontiguousarray(A[:rows])
+    fn = (lambda: oracle.ref_cpu_sparse_gemm_int8(a, B, threads=cores)) if kind == "reference" else \
+         (lambda: oracle.igemm(a, B, threads=cores))
+    fn()
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 or (time.perf_counter() - t0 < 4.0 and reps < 50):
+        fn(); reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 2.0 * rows * N_LOCAL * K / dt / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{rows} of {M} rows of the 4096^3 integer GEMM, x{reps}, {cores} host threads on row slabs"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the sparse / decode side measurements")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiler-friendly run: only warm-up + the timed steps of the headline kernel")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import oracle                      # data generators + the cpu_baseline leg only
+    import bare_metal_b200 as bm
+    from bare_metal_b200 import igemm as ig
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists)")
+    torch.cuda.set_device(local_rank)
+    devn = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=devn)
+    bm.build()
+    peaks = load_peaks()
+
+    # ---- operands: enough rotating sets that consecutive steps never hit L2 (126 MB) -------------
+    n_total = N_LOCAL * world
+    set_bytes = M * K + N_LOCAL * K + 2 * M * N_LOCAL
+    n_sets = max(2, -(-3 * 126 * 2 ** 20 // set_bytes))          # > 3x L2 in flight
+    sid = oracle.stream_id
+    A_h = oracle.gen_int8((M, K), 0, sid("C2", "A"))
+    W_h = oracle.gen_int8((N_LOCAL, K), 0, sid("C2", f"W{rank}"))
+    sa_h = oracle.gen_scales(M, 0, sid("C2", "sa"))
+    sw_h = oracle.gen_scales(N_LOCAL, 0, sid("C2", f"sw{rank}"))
+    A_d = [torch.from_numpy(A_h).to(devn) for _ in range(n_sets)]
+    W_d = [torch.from_numpy(W_h).to(devn) for _ in range(n_sets)]
+    sa_d, sw_d = torch.from_numpy(sa_h).to(devn), torch.from_numpy(sw_h).to(devn)
+    if world == 1:
+        D_d = [torch.empty((M, N_LOCAL), dtype=torch.float16, device=devn) for _ in range(n_sets)]
+        G_d = None
+    else:
+        D_d = [torch.empty((M, N_LOCAL), dtype=torch.float16, device=devn) for _ in range(2)]
+        G_d = [torch.empty((world, M, N_LOCAL), dtype=torch.float16, device=devn) for _ in range(2)]
+
+    def step(i: int):
+        s = i % n_sets
+        if world == 1:
+            ig.w8a8_linear(A_d[s], W_d[s], D_d[s], sa_d, sw_d, M, N_LOCAL, K)
+        else:
+            ig.w8a8_linear(A_d[s], W_d[s], D_d[i % 2], sa_d, sw_d, M, N_LOCAL, K)
+            dist.all_gather_into_tensor(G_d[i % 2], D_d[i % 2])
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- parity of what is being timed (one step against the CPU oracle on sampled rows) -----------
+    step(0)
+    torch.cuda.synchronize()
+    rows = np.array([0, 1, 127, 128, 2047, 4095])
+    want = oracle.dequant_w8a8_f16(oracle.igemm_nt(np.ascontiguousarray(A_h[rows]), W_h), sa_h[rows], sw_h)
+    got = D_d[0].cpu().numpy()[rows]
+    if not np.array_equal(got.view(np.uint16), want.view(np.uint16)):
+        raise SystemExit("parity check failed: the benchmarked kernel disagrees with the CPU oracle")
+
+    # ---- timed region ----------------------------------------------------------------------------
+    for i in range(args.warmup):
+        step(i)
+    sync()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    # keep the region long enough for nvidia-smi to see it: repeat the K steps in rounds
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    t_wall0 = time.time()
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    sync()
+    ms_total = ev0.elapsed_time(ev1)
+    # extra untimed load so the clock sampler has samples under load even for a short region
+    t_load = time.time()
+    j = 0
+    while not args.profile and time.time() - t_load < 0.6:
+        step(j); j += 1
+        if j % 64 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms_total], dtype=torch.float64, device=devn)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    ops_step = 2.0 * M * n_total * K
+    value = ops_step / (ms_step * 1e-3) / 1e12
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "value": value, "unit": UNIT, "ms_per_step": ms_step}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- kernel-only duration for the roofline (the GEMM launch alone, same stream) ----------------
+    ke0, ke1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ke0.record()
+    for i in range(args.steps):
+        s = i % n_sets
+        ig.w8a8_linear(A_d[s], W_d[s], D_d[s % len(D_d)], sa_d, sw_d, M, N_LOCAL, K)
+    ke1.record()
+    torch.cuda.synchronize()
+    kern_ms = ke0.elapsed_time(ke1) / args.steps
+    achieved = 2.0 * M * N_LOCAL * K / (kern_ms * 1e-3) / 1e12
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+                "frac": achieved / int8_peak,
+                "peak_note": f"2 x cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s, of {peaks['source']}); "
+                             f"INT8 runs at twice the bf16 rate on this tensor core",
+                "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
+                "kernel": "igemm_dense_kernel<256,false,EPI_F16_ROWCOL>", "kernel_ms": kern_ms,
+                "algorithmic_bytes": set_bytes,
+                "traffic": TRAFFIC_BYTES_NCU}
+
+    # ---- end to end through the C ABI with host buffers --------------------------------------------
+    e2e = None
+    if rank == 0 or world > 1:
+        pin = lambda a: torch.from_numpy(a).pin_memory()
+        A_p, W_p, sa_p, sw_p = pin(A_h), pin(W_h), pin(sa_h), pin(sw_h)
+        D_p = torch.empty((M, N_LOCAL), dtype=torch.float16).pin_memory()
+        A_e, W_e = torch.empty_like(A_d[0]), torch.empty_like(W_d[0])
+        sa_e, sw_e = torch.empty_like(sa_d), torch.empty_like(sw_d)
+        D_e = torch.empty((M, N_LOCAL), dtype=torch.float16, device=devn)
+
+        def e2e_step():
+            A_e.copy_(A_p, non_blocking=True); W_e.copy_(W_p, non_blocking=True)
+            sa_e.copy_(sa_p, non_blocking=True); sw_e.copy_(sw_p, non_blocking=True)
+            ig.w8a8_linear(A_e, W_e, D_e, sa_e, sw_e, M, N_LOCAL, K)
+            D_p.copy_(D_e, non_blocking=True)
+
+        n_e2e = max(5, min(args.steps, 30))
+        for _ in range(3):
+            e2e_step()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        sync()
+        e_ms = e0.elapsed_time(e1) / n_e2e
+        if world > 1:
+            t = torch.tensor([e_ms], dtype=torch.float64, device=devn)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        if not np.array_equal(D_p.numpy()[rows].view(np.uint16), want.view(np.uint16)):
+            raise SystemExit("parity check failed on the end-to-end path")
+        e2e = {"value": ops_step / (e_ms * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": int(M * K + N_LOCAL * K + 4 * (M + N_LOCAL)),
+               "d2h_bytes_per_step": int(2 * M * N_LOCAL), "ms_per_step": e_ms, "steps": n_e2e,
+               "path": "pinned host -> cudaMemcpyAsync -> bm_w8a8_f16 -> cudaMemcpyAsync -> pinned host"}
+
+    # ---- side measurements: 2:4 sparse 4096^3 and the decode shapes (not the headline) -------------
+    extras = {}
+    if rank == 0 and not args.no_extras:
+        extras = side_measurements(ig, oracle, torch, devn, peaks)
+
+    if rank == 0:
+        cpu = None if args.no_cpu_baseline else cpu_baseline_leg()
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "s8*s8->s32 (fp32 scale, fp16 out)", "data": "synthetic",
+                "config": {"workload": f"C2 W8A8 GEMM M={M} K={K} N={n_total} ({N_LOCAL} weight columns per GPU)",
+                           "parallelism": f"n-split x{world}" + ("" if world == 1 else " + NCCL all-gather of the fp16 output"),
+                           "l2": f"{n_sets} rotating operand sets ({n_sets * set_bytes / 2**20:.0f} MiB) exceed the 126 MiB L2",
+                           "tile": "128x256x128, 4-stage TMA ring, 2 TMEM accumulators"},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps,
+                "clocks": clocks, "extras": extras}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the benchmarked kernel, from the
+# committed ncu capture (profiles/); None until one exists for this kernel build.
+TRAFFIC_BYTES_NCU = None
+
+
+def side_measurements(ig, oracle, torch, devn, peaks):
+    """2:4-sparse 4096^3 (config 3) and decode-shaped sparse GEMV (config 5): reported beside the
+    headline, each with its own roofline fraction."""
+    out = {}
+
+    def timeit(fn, iters, warm=5):
+        for i in range(warm):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    sid = oracle.stream_id
+    # config 3
+    Ms = Ns = Ks = 4096
+    comp, nib = oracle.gen_sparse_rows(Ns, Ks, 0, sid("C3", "W"))
+    X = oracle.gen_int8((Ms, Ks), 0, sid("C3", "A"))
+    sets = 6
+    comp_d = [torch.from_numpy(comp).to(devn) for _ in range(sets)]
+    til_d = [ig.sp_pack_meta(torch.from_numpy(nib).to(devn), ig.BM_META_ROWS, Ns, Ks) for _ in range(sets)]
+    X_d = [torch.from_numpy(X).to(devn) for _ in range(sets)]
+    C_d = [torch.empty((Ms, Ns), dtype=torch.int32, device=devn) for _ in range(sets)]
+    ms = timeit(lambda i: ig.w8a8_sparse_i32(X_d[i % sets], comp_d[i % sets], til_d[i % sets], C_d[i % sets], Ms, Ns, Ks), 100)
+    out["sparse_2to4_4096"] = {"ms": ms, "dense_equiv_tops": 2.0 * Ms * Ns * Ks / ms / 1e9,
+                               "l2": f"{sets} rotating operand sets"}
+    del comp_d, til_d, X_d, C_d
+    # config 5
+    Nd, Kd = 28672, 8192
+    comp, nib = oracle.gen_sparse_rows(Nd, Kd, 0, sid("C5", "W"))
+    comp_d = [torch.from_numpy(comp).to(devn) for _ in range(2)]       # 2 x 147 MB > L2
+    til_d = [ig.sp_pack_meta(torch.from_numpy(nib).to(devn), ig.BM_META_ROWS, Nd, Kd) for _ in range(2)]
+    sw = torch.from_numpy(oracle.gen_scales(Nd, 0, sid("C5", "sw"))).to(devn)
+    dec = {}
+    for Md in (1, 16, 64):
+        Xd = torch.from_numpy(oracle.gen_int8((Md, Kd), 0, sid("C5", f"X{Md}"))).to(devn)
+        sa = torch.from_numpy(oracle.gen_scales(Md, 0, sid("C5", "sa"))).to(devn)
+        Dd = torch.empty((Md, Nd), dtype=torch.float16, device=devn)
+        ms = timeit(lambda i: ig.w8a8_sparse_linear(Xd, comp_d[i % 2], til_d[i % 2], Dd, sa, sw, Md, Nd, Kd), 60)
+        byts = Nd * Kd / 2 + Nd * Kd / 8 + Md * Kd + 2 * Md * Nd + 4 * (Md + Nd)
+        gbs = byts / ms / 1e6
+        dec[f"M{Md}"] = {"us": ms * 1e3, "algorithmic_bytes": byts, "gb_per_s": gbs,
+                         "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+    out["decode_sparse_K8192_N28672"] = dec
+    out["hbm_peak_gbs"] = peaks["hbm_gbs"]
+    return out
+
+
+if __name__ == "__main__":
+    main()

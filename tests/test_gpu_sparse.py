@@ -1,0 +1,145 @@
+"""2:4 structured-sparse INT8 GEMM on the GPU against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from bare_metal_b200 import igemm as ig
+from _gpu import T, assert_clean_status, dev, forced_bn, ulp_diff_f16
+
+pytestmark = pytest.mark.gpu
+
+
+def bench_sparse_inputs(M, N, K):
+    """bench_sparse.cu:52-64: generator seed 42, reference compressor, scales 1/127."""
+    dense = oracle.gen_sparse_2_4_ref(M, K, 42)
+    comp, meta = oracle.compress_2_4_ref(dense)
+    B = oracle.gen_int8((K, N), 137, 1)
+    B[B == 0] = 1                                  # the bench draws non-zero B (bench_sparse.cu:55-60)
+    return dense, comp, meta, B
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (512, 512, 512), (128, 16, 32), (144, 272, 1056)])
+def test_reference_sparse_kernel_abi(M, N, K):
+    """igemm_sparse_tiled's ABI and acceptance test: fp32 out vs exact int32 CPU GEMM * (1/127)^2."""
+    dense, comp, meta, B = bench_sparse_inputs(M, N, K)
+    s = np.float32(1.0) / np.float32(127.0)
+    C = torch.full((M, N), -1.0, dtype=torch.float32, device=dev())
+    ig.igemm_sparse_tiled(T(comp), T(B), C, T(meta.view(np.int32)), M, N, K, float(s), float(s))
+    assert_clean_status()
+    want = oracle.dequant_per_tensor(oracle.igemm(dense, B, threads=0), s, s)
+    got = C.cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    r = oracle.check_fp32(got, want, 0.5, 0.1)
+    assert r["num_errors"] == 0 and r["max_abs"] == 0.0        # the reference fixture shows max_abs=0
+
+
+def test_golden_sparse_vectors_from_the_reference_build(golden):
+    """Inputs AND outputs produced by the reference's own CPU code (tests/golden)."""
+    for (M, K) in ((32, 64), (48, 128)):
+        comp, meta = golden[f"sp_comp_{M}x{K}"], golden[f"sp_meta_{M}x{K}"]
+        B, want = golden[f"sp_b_{M}x{K}"], golden[f"sp_c_{M}x{K}"]
+        N = B.shape[1]
+        Bp = np.zeros((K, 32), np.int8)             # pad N 24 -> 32 for the 16-byte pitch rule
+        Bp[:, :N] = B
+        C = torch.zeros((M, 32), dtype=torch.int32, device=dev())
+        ig.igemm_sparse_i32(T(comp), T(meta.view(np.int32)), ig.BM_META_REF, T(Bp), C, M, 32, K, ig.BM_B_KN)
+        assert_clean_status()
+        assert np.array_equal(C.cpu().numpy()[:, :N], want)
+
+
+def test_known_answer_all_ones():
+    """tests/hgemm_sparse/test_mma_sp.cu pattern: all-ones operands, metadata 0x44444444
+    (positions 0,1 in every group) -> every output equals K/2."""
+    M, N, K = 128, 128, 512
+    comp = np.ones((M, K // 2), np.int8)
+    meta = np.full(oracle.sparse_meta_count(M, K), 0x44444444, np.uint32)
+    B = np.ones((K, N), np.int8)
+    C = torch.zeros((M, N), dtype=torch.int32, device=dev())
+    ig.igemm_sparse_i32(T(comp), T(meta.view(np.int32)), ig.BM_META_REF, T(B), C, M, N, K, ig.BM_B_KN)
+    assert_clean_status()
+    assert (C.cpu().numpy() == K // 2).all()
+    # position decode: B[k][:] = k % 4 makes the output the sum of the selected positions
+    Bpos = (np.arange(K) % 4).astype(np.int8)[:, None].repeat(N, 1)
+    for nibble, s in ((0x4, 0 + 1), (0xE, 2 + 3), (0x9, 1 + 2), (0xC, 0 + 3)):
+        word = sum(nibble << (4 * i) for i in range(8))
+        meta[:] = word
+        ig.igemm_sparse_i32(T(comp), T(meta.view(np.int32)), ig.BM_META_REF, T(Bpos), C, M, N, K, ig.BM_B_KN)
+        assert (C.cpu().numpy() == s * (K // 4)).all()
+
+
+@pytest.mark.parametrize("layout", [ig.BM_B_NK, ig.BM_B_KN])
+@pytest.mark.parametrize("M,N,K,bn", [(128, 128, 256, 128), (128, 256, 256, 256), (128, 128, 64, 128),
+                                      (256, 256, 512, 128), (128, 64, 256, 64), (272, 400, 1056, None),
+                                      (512, 512, 1024, None)])
+def test_sparse_left_rows_format(layout, M, N, K, bn):
+    """Independent 6-pattern sparsity per row (no r/r+8 sharing), per-row nibble metadata."""
+    if layout == ig.BM_B_KN and bn == 64:
+        bn = 128
+    comp, nib = oracle.gen_sparse_rows(M, K, 0, 11)
+    B = oracle.gen_int8((K, N), 0, 12)
+    want = oracle.igemm(oracle.decompress_rows(comp, nib), B, threads=0)
+    C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
+    with forced_bn(bn):
+        ig.igemm_sparse_i32(T(comp), T(nib), ig.BM_META_ROWS, T(B) if layout == ig.BM_B_KN else T(B.T),
+                            C, M, N, K, layout)
+    assert_clean_status()
+    assert np.array_equal(C.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(16, 128, 256, 16), (1, 256, 512, 16), (32, 128, 256, 32), (64, 256, 512, 64),
+                                      (128, 256, 512, 128), (256, 384, 1024, 256), (100, 200, 288, None),
+                                      (3, 136, 96, None), (64, 1024, 2048, None), (300, 520, 800, None)])
+def test_sparse_weights_i32_and_f16(M, N, K, bn):
+    """Sparse WEIGHTS W[N,K] (config 3/5 convention): C = X @ W^T, int32 bit-exact, fp16 <= 1 ulp."""
+    comp, nib = oracle.gen_sparse_rows(N, K, 0, 21)
+    X = oracle.gen_int8((M, K), 0, 22)
+    want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
+    tiled = ig.sp_pack_meta(T(nib), ig.BM_META_ROWS, N, K)
+    guard = torch.full((M + 2, N), 0x5A5A5A5A, dtype=torch.int32, device=dev())
+    C = guard[1:M + 1]
+    with forced_bn(bn):
+        ig.w8a8_sparse_i32(T(X), T(comp), tiled, C, M, N, K)
+    assert_clean_status()
+    g = guard.cpu().numpy()
+    assert np.array_equal(g[1:M + 1], want)
+    assert (g[0] == 0x5A5A5A5A).all() and (g[-1] == 0x5A5A5A5A).all()
+    sa, sw = oracle.gen_scales(M, 0, 3), oracle.gen_scales(N, 0, 4)
+    D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+    with forced_bn(bn):
+        ig.w8a8_sparse_linear(T(X), T(comp), tiled, D, T(sa), T(sw), M, N, K)
+    assert_clean_status()
+    assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)) <= 1
+
+
+def test_metadata_repack_formats_agree():
+    """Reference uint32 words and per-row nibbles describe the same positions -> same tiled bytes."""
+    M, K = 272, 800
+    dense = oracle.gen_sparse_2_4_ref(M, K, 42)
+    comp, meta = oracle.compress_2_4_ref(dense)
+    nib = oracle.meta_ref_to_rows(meta, M, K)
+    t_ref = ig.sp_pack_meta(T(meta.view(np.int32)), ig.BM_META_REF, M, K).cpu().numpy()
+    t_rows = ig.sp_pack_meta(T(nib), ig.BM_META_ROWS, M, K).cpu().numpy()
+    assert np.array_equal(t_ref, t_rows)
+    # tiled order: [row block][k block][chunk][row][16 bytes]; padding is the valid pattern 0x44
+    kb = (K + 255) // 256
+    t = t_rows.reshape((M + 127) // 128, kb, 2, 128, 16)
+    rows = t.transpose(0, 3, 1, 2, 4).reshape(-1, kb * 32)
+    assert np.array_equal(rows[:M, :K // 8], nib)
+    assert (rows[M:] == 0x44).all() and (rows[:M, K // 8:] == 0x44).all()
+
+
+def test_sparse_repeat_launches_are_bit_identical():
+    M, N, K = 64, 2048, 4096
+    comp, nib = oracle.gen_sparse_rows(N, K, 1, 21)
+    X = T(oracle.gen_int8((M, K), 1, 22))
+    compd, tiled = T(comp), ig.sp_pack_meta(T(nib), ig.BM_META_ROWS, N, K)
+    first = None
+    for i in range(30):
+        C = torch.empty((M, N), dtype=torch.int32, device=dev())
+        ig.w8a8_sparse_i32(X, compd, tiled, C, M, N, K)
+        if first is None:
+            first = C.clone()
+        else:
+            assert torch.equal(C, first), f"launch {i} differs"
+    assert_clean_status()
