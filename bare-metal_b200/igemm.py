@@ -33,6 +33,17 @@ def _dev(t: torch.Tensor, dtype, name: str) -> int:
     return t.data_ptr()
 
 
+def _out(t: torch.Tensor, dtype, name: str) -> int:
+    """Output buffers may be strided views (a column slab of a wider matrix): unit inner stride."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise BmError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise BmError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if t.dim() == 2 and t.stride(1) != 1:
+        raise BmError(f"{name} must have unit stride along its rows")
+    return t.data_ptr()
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -43,7 +54,7 @@ def _stream() -> int:
 def igemm_wmma(A, B, C, M, N, K, scale_a, scale_b, b_layout=BM_B_KN):
     """C[M,N] fp32 = float(A[M,K] @ B[K,N]) * (scale_a * scale_b)."""
     L = _lib.load()
-    rc = L.bm_igemm_i8_f32(_dev(A, torch.int8, "A"), _dev(B, torch.int8, "B"), _dev(C, torch.float32, "C"),
+    rc = L.bm_igemm_i8_f32(_dev(A, torch.int8, "A"), _dev(B, torch.int8, "B"), _out(C, torch.float32, "C"),
                            M, N, K, scale_a, scale_b, C.stride(0) if C.dim() == 2 else N, b_layout, _stream())
     _lib.check(rc, "bm_igemm_i8_f32")
     return C
@@ -64,7 +75,7 @@ def igemm_pipelined_cpasync_perchannel(A, B, C, M, N, K, per_channel_scale, per_
     """C[m,n] = (float(acc) - float(zp[n])) * scale[n] — igemm_pipelined_cpasync_perchannel.cu:48-56."""
     L = _lib.load()
     rc = L.bm_igemm_i8_f32_perchannel(_dev(A, torch.int8, "A"), _dev(B, torch.int8, "B"),
-                                      _dev(C, torch.float32, "C"), M, N, K,
+                                      _out(C, torch.float32, "C"), M, N, K,
                                       _dev(per_channel_scale, torch.float32, "scale"),
                                       _dev(per_channel_zero_point, torch.int32, "zero_point"),
                                       C.stride(0) if C.dim() == 2 else N, b_layout, _stream())
@@ -93,7 +104,7 @@ def igemm_sparse_tiled_persistent(A_comp, B, C, meta, M, N, K, scale_a, scale_b,
 def igemm_i32(A, B, C, M, N, K, b_layout=BM_B_KN):
     """Raw int32 accumulators C[M,N] = A[M,K] @ B (B[K,N], or W[N,K] with BM_B_NK)."""
     L = _lib.load()
-    rc = L.bm_igemm_i8_i32(_dev(A, torch.int8, "A"), _dev(B, torch.int8, "B"), _dev(C, torch.int32, "C"),
+    rc = L.bm_igemm_i8_i32(_dev(A, torch.int8, "A"), _dev(B, torch.int8, "B"), _out(C, torch.int32, "C"),
                            M, N, K, C.stride(0) if C.dim() == 2 else N, b_layout, _stream())
     _lib.check(rc, "bm_igemm_i8_i32")
     return C
@@ -137,7 +148,7 @@ def sp_pack_meta(meta, meta_format, R, K):
 def igemm_sparse_i32(A_comp, meta, meta_format, B, C, M, N, K, b_layout=BM_B_KN):
     L = _lib.load()
     rc = L.bm_igemm_sparse_i32(_dev(A_comp, torch.int8, "A_comp"), meta.data_ptr(), meta_format,
-                               _dev(B, torch.int8, "B"), _dev(C, torch.int32, "C"), M, N, K,
+                               _dev(B, torch.int8, "B"), _out(C, torch.int32, "C"), M, N, K,
                                C.stride(0) if C.dim() == 2 else N, b_layout, _stream())
     _lib.check(rc, "bm_igemm_sparse_i32")
     return C
@@ -146,7 +157,7 @@ def igemm_sparse_i32(A_comp, meta, meta_format, B, C, M, N, K, b_layout=BM_B_KN)
 def w8a8_sparse_i32(X, W_comp, W_meta_tiled, C, M, N, K):
     L = _lib.load()
     rc = L.bm_w8a8_sparse_i32(_dev(X, torch.int8, "X"), _dev(W_comp, torch.int8, "W_comp"),
-                              _dev(W_meta_tiled, torch.uint8, "W_meta"), _dev(C, torch.int32, "C"), M, N, K,
+                              _dev(W_meta_tiled, torch.uint8, "W_meta"), _out(C, torch.int32, "C"), M, N, K,
                               C.stride(0) if C.dim() == 2 else N, _stream())
     _lib.check(rc, "bm_w8a8_sparse_i32")
     return C
