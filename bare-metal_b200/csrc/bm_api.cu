@@ -5,6 +5,7 @@
 
 #include "host_common.cuh"
 #include "igemm_dense.cuh"
+#include "igemm_dense_pair.cuh"
 #include "igemm_sparse.cuh"
 #include "pack_kernels.cuh"
 
@@ -34,8 +35,8 @@ static size_t out_elem_size(int epi) { return epi == EPI_F16_ROWCOL ? 2 : 4; }
 // dense
 // =========================================================================================
 template <int BN, bool B_MN, int EPI>
-static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const DenseParams& p, int grid,
-                             cudaStream_t stream) {
+static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+                             const DenseParams& p, int grid, cudaStream_t stream) {
     using Cfg = DenseCfg<BN>;
     auto kern = igemm_dense_kernel<BN, B_MN, EPI>;
     static bool configured[kMaxDevices] = {};
@@ -45,19 +46,53 @@ static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured[dev] = true;
     }
-    kern<<<grid, kDenseThreads, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
+    kern<<<grid, kDenseThreads, Cfg::SMEM_BYTES, stream>>>(ma, mb, mo, p);
     BM_CUDA_TRY(cudaGetLastError());
     return BM_OK;
 }
 
+// CTA-pair kernel: 2-CTA clusters, one pair per two SMs, 256 x 256 tiles
 template <bool B_MN, int EPI>
-static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const DenseParams& p, int grid,
-                           cudaStream_t stream) {
+static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+                             const DenseParams& p, int pairs, cudaStream_t stream) {
+    auto kern = igemm_dense_pair_kernel<B_MN, EPI>;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    BM_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev]) {
+        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kDenseThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, mo, p));
+    return BM_OK;
+}
+
+// BM_DENSE_PAIR=0 keeps large problems on the single-CTA kernel (testing hook; default on)
+static bool pair_enabled() {
+    const char* e = getenv("BM_DENSE_PAIR");
+    return !e || atoi(e) != 0;
+}
+
+template <bool B_MN, int EPI>
+static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+                           const DenseParams& p, int grid, cudaStream_t stream) {
     switch (bn) {
-        case 256: return launch_dense_inst<256, B_MN, EPI>(ma, mb, p, grid, stream);
-        case 128: return launch_dense_inst<128, B_MN, EPI>(ma, mb, p, grid, stream);
+        case 256: return launch_dense_inst<256, B_MN, EPI>(ma, mb, mo, p, grid, stream);
+        case 128: return launch_dense_inst<128, B_MN, EPI>(ma, mb, mo, p, grid, stream);
         case 64:
-            if constexpr (!B_MN) return launch_dense_inst<64, B_MN, EPI>(ma, mb, p, grid, stream);
+            if constexpr (!B_MN) return launch_dense_inst<64, B_MN, EPI>(ma, mb, mo, p, grid, stream);
         default: return fail_msg(BM_ERR_SHAPE, "unsupported tile width");
     }
 }
@@ -90,12 +125,14 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
     }
     if (b_mn && bn < 128) bn = 128;
 
+    const bool use_pair = (bn == 256) && pair_enabled() && dev->sm_count >= 2;
+
     CUtensorMap map_a, map_b;
     if (int rc = make_tensor_map_u8(&map_a, A, K, M, K, kBK, kBM, true)) return rc;
     if (b_mn) {
         if (int rc = make_tensor_map_u8(&map_b, B, N, K, N, 128, kBK, true)) return rc;
     } else {
-        if (int rc = make_tensor_map_u8(&map_b, B, K, N, K, kBK, bn, true)) return rc;
+        if (int rc = make_tensor_map_u8(&map_b, B, K, N, K, kBK, use_pair ? kPairHalfN : bn, true)) return rc;
     }
 
     DenseParams p{};
@@ -108,20 +145,44 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
     p.epi.col_scale = col_scale;
     p.epi.col_zero = col_zero;
     p.epi.vec_ok = aligned16(C) && (static_cast<size_t>(ldc) * out_elem_size(epi)) % 16 == 0;
+    CUtensorMap map_out{};
+    if (p.epi.vec_ok && !getenv("BM_NO_TMA_STORE")) {
+        if (int rc = make_tensor_map_out(&map_out, C, N, M, static_cast<size_t>(ldc) * out_elem_size(epi),
+                                         static_cast<int>(out_elem_size(epi))))
+            return rc;
+        p.epi.tma_ok = 1;
+    }
     p.tiles_m = tiles_m;
     p.tiles_n = ceil_div(N, bn);
     p.k_blocks = ceil_div(K, kBK);
     p.status = dev->status;
-    if (const char* e = getenv("BM_DBG_LBO")) p.dbg_lbo = atoi(e);
-    if (const char* e = getenv("BM_DBG_SBO")) p.dbg_sbo = atoi(e);
+    if (const char* e = getenv("BM_DBG_BUF")) p.dbg_buf = reinterpret_cast<unsigned long long*>(strtoull(e, nullptr, 0));
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int grid = num_tiles < dev->sm_count ? num_tiles : dev->sm_count;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
+    if (use_pair) {
+        p.tiles_m = ceil_div(M, 256);
+        const int pair_tiles = p.tiles_m * p.tiles_n;
+        const int max_pairs = dev->sm_count / 2;
+        const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+#define BM_PAIR_CASE(E)                                                                         \
+    case E:                                                                                     \
+        return b_mn ? launch_dense_pair<true, E>(map_a, map_b, map_out, p, pairs, stream)       \
+                    : launch_dense_pair<false, E>(map_a, map_b, map_out, p, pairs, stream);
+        switch (epi) {
+            BM_PAIR_CASE(EPI_I32)
+            BM_PAIR_CASE(EPI_F32_TENSOR)
+            BM_PAIR_CASE(EPI_F32_CHANNEL)
+            BM_PAIR_CASE(EPI_F16_ROWCOL)
+        }
+#undef BM_PAIR_CASE
+    }
+
 #define BM_DENSE_CASE(E)                                                                        \
     case E:                                                                                     \
-        return b_mn ? launch_dense_bn<true, E>(bn, map_a, map_b, p, grid, stream)               \
-                    : launch_dense_bn<false, E>(bn, map_a, map_b, p, grid, stream);
+        return b_mn ? launch_dense_bn<true, E>(bn, map_a, map_b, map_out, p, grid, stream)      \
+                    : launch_dense_bn<false, E>(bn, map_a, map_b, map_out, p, grid, stream);
     switch (epi) {
         BM_DENSE_CASE(EPI_I32)
         BM_DENSE_CASE(EPI_F32_TENSOR)
@@ -172,7 +233,7 @@ static int launch_sparse_inst(const CUtensorMap& ms, const CUtensorMap& md, cons
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured[dev] = true;
     }
-    kern<<<grid, kSpThreads, Cfg::SMEM_BYTES, stream>>>(ms, md, p);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ms, md, p);
     BM_CUDA_TRY(cudaGetLastError());
     return BM_OK;
 }

@@ -11,9 +11,17 @@
 //                    (igemm_pipelined_cpasync_perchannel.cu:276-281)
 //   EPI_F16_ROWCOL   D = half_rn((float)acc * (sa[m] * sw[n]))
 // __fmul_rn / __fsub_rn keep the compiler from contracting anything into an FMA.
+//
+// Latency structure: the parameters that vary along the accumulator COLUMNS of a tile (sw[n] and
+// zp[n] in the normal orientation, sa[m] in the transposed one) are staged once per tile into a
+// per-warp strip of shared memory BEFORE the warp waits for the accumulator, and the tensor-
+// memory loads are double-buffered (chunk c+1 is in flight while chunk c is converted), so the
+// drain of a tile is a short dependent chain instead of eight.
 #pragma once
 #include <cstdint>
 #include <cuda_fp16.h>
+
+#include "sm100_ptx.cuh"
 
 namespace bm {
 
@@ -28,6 +36,7 @@ struct EpilogueParams {
     const float* col_scale;    // EPI_F16_ROWCOL : sw[cols];  EPI_F32_CHANNEL : scale[cols]
     const int* col_zero;       // EPI_F32_CHANNEL : zero_point[cols]
     int vec_ok;                // output base and pitch allow 16-byte vector stores
+    int tma_ok;                // ... and a tensor map of the output exists: drain through TMA stores
 };
 
 template <int EPI>
@@ -37,30 +46,63 @@ struct OutType<EPI_I32> { using type = int32_t; };
 template <>
 struct OutType<EPI_F16_ROWCOL> { using type = __half; };
 
+// `lane_s` is the scale attached to the accumulator lane, `cross_s` / `cross_z` the scale and
+// zero point attached to the accumulator column (fp32 multiplication commutes, so the product
+// sa*sw has the same bits in either orientation).
 template <int EPI>
 __device__ __forceinline__ typename OutType<EPI>::type
-convert_one(const EpilogueParams& p, int32_t acc, int row, int col, float row_s) {
+convert_acc(int32_t acc, float tensor_scale, float lane_s, float cross_s, int cross_z) {
     if constexpr (EPI == EPI_I32) {
         return acc;
     } else if constexpr (EPI == EPI_F32_TENSOR) {
-        return __fmul_rn(__int2float_rn(acc), p.tensor_scale);
+        return __fmul_rn(__int2float_rn(acc), tensor_scale);
     } else if constexpr (EPI == EPI_F32_CHANNEL) {
-        return __fmul_rn(__fsub_rn(__int2float_rn(acc), __int2float_rn(__ldg(p.col_zero + col))),
-                         __ldg(p.col_scale + col));
+        return __fmul_rn(__fsub_rn(__int2float_rn(acc), __int2float_rn(cross_z)), cross_s);
     } else {
-        float s = __fmul_rn(row_s, __ldg(p.col_scale + col));
-        return __float2half_rn(__fmul_rn(__int2float_rn(acc), s));
+        return __float2half_rn(__fmul_rn(__int2float_rn(acc), __fmul_rn(lane_s, cross_s)));
     }
 }
 
-// Lane = output ROW.  The thread holds columns [col0, col0+32) of row `row`.
+// Per-warp strip of column-side parameters for NC accumulator columns.
+template <int NC>
+struct EpiStrip {
+    float scale[NC];
+    int zero[NC];
+};
+
+// Fill the strip for accumulator columns [cross0, cross0 + NC) of the coming tile.
+template <int EPI, int NC, bool TRANSPOSED>
+__device__ __forceinline__ void stage_strip(const EpilogueParams& p, EpiStrip<NC>* strip, int cross0, int lane) {
+    if constexpr (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) {
+        const float* src = TRANSPOSED ? p.row_scale : p.col_scale;
+        const int limit = TRANSPOSED ? p.rows : p.cols;
+#pragma unroll
+        for (int i = lane; i < NC; i += 32) {
+            const int c = cross0 + i;
+            strip->scale[i] = c < limit ? __ldg(src + c) : 0.f;
+            if constexpr (EPI == EPI_F32_CHANNEL) strip->zero[i] = c < limit ? __ldg(p.col_zero + c) : 0;
+        }
+        __syncwarp();
+    }
+}
+
+template <int EPI, bool TRANSPOSED>
+__device__ __forceinline__ float lane_scale_of(const EpilogueParams& p, int lane_coord) {
+    if constexpr (EPI == EPI_F16_ROWCOL) {
+        const float* src = TRANSPOSED ? p.col_scale : p.row_scale;
+        const int limit = TRANSPOSED ? p.cols : p.rows;
+        return lane_coord < limit ? __ldg(src + lane_coord) : 0.f;
+    } else {
+        return 0.f;
+    }
+}
+
+// Normal orientation: the thread holds columns [col0, col0+32) of output row `row`.
 template <int EPI>
-__device__ __forceinline__ void store_row_chunk(const EpilogueParams& p, int row, int col0,
-                                                const uint32_t (&r)[32]) {
+__device__ __forceinline__ void emit_row_chunk(const EpilogueParams& p, int row, int col0, const uint32_t (&r)[32],
+                                               const float* s_scale, const int* s_zero, float lane_s) {
     using T = typename OutType<EPI>::type;
     if (row >= p.rows || col0 >= p.cols) return;
-    float row_s = 0.f;
-    if constexpr (EPI == EPI_F16_ROWCOL) row_s = __ldg(p.row_scale + row);
     T* dst = reinterpret_cast<T*>(p.out) + static_cast<long long>(row) * p.ld + col0;
     if (p.vec_ok && col0 + 32 <= p.cols) {
         constexpr int PER_VEC = 16 / sizeof(T);
@@ -68,35 +110,139 @@ __device__ __forceinline__ void store_row_chunk(const EpilogueParams& p, int row
         for (int v = 0; v < 32 / PER_VEC; ++v) {
             alignas(16) T tmp[PER_VEC];
 #pragma unroll
-            for (int j = 0; j < PER_VEC; ++j)
-                tmp[j] = convert_one<EPI>(p, static_cast<int32_t>(r[v * PER_VEC + j]), row,
-                                          col0 + v * PER_VEC + j, row_s);
+            for (int j = 0; j < PER_VEC; ++j) {
+                const int k = v * PER_VEC + j;
+                tmp[j] = convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s,
+                                          (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) ? s_scale[k] : 0.f,
+                                          EPI == EPI_F32_CHANNEL ? s_zero[k] : 0);
+            }
             *reinterpret_cast<uint4*>(dst + v * PER_VEC) = *reinterpret_cast<const uint4*>(tmp);
         }
     } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.cols)
-                dst[j] = convert_one<EPI>(p, static_cast<int32_t>(r[j]), row, col0 + j, row_s);
+        for (int k = 0; k < 32; ++k)
+            if (col0 + k < p.cols)
+                dst[k] = convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s,
+                                          (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) ? s_scale[k] : 0.f,
+                                          EPI == EPI_F32_CHANNEL ? s_zero[k] : 0);
     }
 }
 
-// Lane = output COLUMN (channel); the 32 accumulator columns are 32 consecutive output ROWS
-// (tokens).  For a fixed token the 32 lanes of a warp write 32 adjacent channels.
+// Transposed orientation: the thread holds output column `col` (a channel) for the 32
+// consecutive output rows (tokens) [row0, row0+32); per token the 32 lanes of the warp write 32
+// adjacent channels.  `row_limit` clips to the tile's own tokens for tiles narrower than 32.
 template <int EPI>
-__device__ __forceinline__ void store_col_chunk(const EpilogueParams& p, int col, int row0,
-                                                const uint32_t (&r)[32]) {
+__device__ __forceinline__ void emit_col_chunk(const EpilogueParams& p, int col, int row0, int row_limit,
+                                               const uint32_t (&r)[32], const float* s_scale, float lane_s) {
     using T = typename OutType<EPI>::type;
     if (col >= p.cols) return;
     T* dst = reinterpret_cast<T*>(p.out) + col;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        int row = row0 + j;
-        if (row < p.rows) {
-            float row_s = 0.f;
-            if constexpr (EPI == EPI_F16_ROWCOL) row_s = __ldg(p.row_scale + row);
+    for (int k = 0; k < 32; ++k) {
+        const int row = row0 + k;
+        if (row < row_limit)
             dst[static_cast<long long>(row) * p.ld] =
-                convert_one<EPI>(p, static_cast<int32_t>(r[j]), row, col, row_s);
+                convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s,
+                                 EPI == EPI_F16_ROWCOL ? s_scale[k] : 0.f, 0);
+    }
+}
+
+// Drain NC accumulator columns starting at tensor-memory address `taddr` (lane quarter and first
+// column already applied).  `cross0` is the output coordinate of the first column.
+template <int EPI, int NC, bool TRANSPOSED>
+__device__ __forceinline__ void drain_accumulator(const EpilogueParams& p, uint32_t taddr, int lane_coord, int cross0,
+                                                  int cross_limit, const EpiStrip<NC>* strip, float lane_s) {
+    static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
+    constexpr int CHUNKS = NC / 32;
+    uint32_t ra[32], rb[32];
+    if (cross0 < cross_limit) tmem_ld_32x32(taddr, ra);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c += 2) {
+        if (cross0 + c * 32 < cross_limit) {                       // warp-uniform
+            tmem_ld_wait();
+            if (c + 1 < CHUNKS && cross0 + (c + 1) * 32 < cross_limit) tmem_ld_32x32(taddr + (c + 1) * 32, rb);
+            if constexpr (TRANSPOSED)
+                emit_col_chunk<EPI>(p, lane_coord, cross0 + c * 32, cross_limit, ra, strip->scale + c * 32, lane_s);
+            else
+                emit_row_chunk<EPI>(p, lane_coord, cross0 + c * 32, ra, strip->scale + c * 32, strip->zero + c * 32, lane_s);
+        }
+        if (c + 1 < CHUNKS && cross0 + (c + 1) * 32 < cross_limit) {
+            tmem_ld_wait();
+            if (c + 2 < CHUNKS && cross0 + (c + 2) * 32 < cross_limit) tmem_ld_32x32(taddr + (c + 2) * 32, ra);
+            if constexpr (TRANSPOSED)
+                emit_col_chunk<EPI>(p, lane_coord, cross0 + (c + 1) * 32, cross_limit, rb, strip->scale + (c + 1) * 32, lane_s);
+            else
+                emit_row_chunk<EPI>(p, lane_coord, cross0 + (c + 1) * 32, rb, strip->scale + (c + 1) * 32,
+                                    strip->zero + (c + 1) * 32, lane_s);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// TMA-store drain (normal orientation).  Direct stores from the accumulator layout make every
+// lane of a warp write a different output ROW (16 bytes each, a pitch apart); with power-of-two
+// pitches those land on few L2 slices and the drain, not the MMA, bounds the tile.  Here each warp
+// converts a 32-row x 128-byte box into a 4 KiB strip of shared memory (128-byte swizzle, so the
+// 16-byte pieces of 8 rows never share a bank) and one lane hands it to the TMA engine, which writes
+// whole 128-byte lines and clips rows/columns beyond the output.  The strip is single-buffered:
+// before it is rewritten the lane waits until the previous store has finished reading it.
+// ------------------------------------------------------------------------------------------------
+constexpr int kStoreBoxBytes = 32 * 128;          // per-warp staging strip
+
+template <int EPI, int NC>
+__device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const CUtensorMap* map_out, uint32_t taddr,
+                                                      int row0, int lane, int col0, const EpiStrip<NC>* strip,
+                                                      float lane_s, uint32_t stage_smem) {
+    using T = typename OutType<EPI>::type;
+    static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
+    constexpr int CHUNKS = NC / 32;
+    constexpr int COLS_PER_BOX = 128 / sizeof(T);            // 64 fp16 or 32 fp32/int32 columns
+    constexpr int CHUNKS_PER_BOX = COLS_PER_BOX / 32;        // 2 or 1
+    constexpr int PIECES_PER_CHUNK = 32 * sizeof(T) / 16;    // 16-byte pieces a thread writes per chunk
+    constexpr int PER_VEC = 16 / sizeof(T);
+    const uint32_t my_row = stage_smem + lane * 128;
+    const int sw = lane & 7;                                 // 128-byte swizzle: piece index ^ (row % 8)
+
+    uint32_t rr[2][32];
+    if (col0 < p.cols) tmem_ld_32x32(taddr, rr[0]);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int cur = c & 1;
+        const bool live = col0 + c * 32 < p.cols;            // warp-uniform
+        if (live) {
+            tmem_ld_wait();
+            if (c + 1 < CHUNKS && col0 + (c + 1) * 32 < p.cols) tmem_ld_32x32(taddr + (c + 1) * 32, rr[cur ^ 1]);
+            if (c % CHUNKS_PER_BOX == 0) {
+                // the strip may still be read by the previous box's store
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+            }
+#pragma unroll
+            for (int v = 0; v < PIECES_PER_CHUNK; ++v) {
+                alignas(16) T tmp[PER_VEC];
+#pragma unroll
+                for (int j = 0; j < PER_VEC; ++j) {
+                    const int k = v * PER_VEC + j;
+                    tmp[j] = convert_acc<EPI>(static_cast<int32_t>(rr[cur][k]), p.tensor_scale, lane_s,
+                                              (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) ? strip->scale[c * 32 + k] : 0.f,
+                                              EPI == EPI_F32_CHANNEL ? strip->zero[c * 32 + k] : 0);
+                }
+                const int piece = (c % CHUNKS_PER_BOX) * PIECES_PER_CHUNK + v;
+                const uint4 val = *reinterpret_cast<const uint4*>(tmp);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + ((piece ^ sw) << 4)), "r"(val.x),
+                             "r"(val.y), "r"(val.z), "r"(val.w)
+                             : "memory");
+            }
+        }
+        const bool box_done = (c % CHUNKS_PER_BOX == CHUNKS_PER_BOX - 1) || c == CHUNKS - 1;
+        const int box_c0 = col0 + (c / CHUNKS_PER_BOX) * COLS_PER_BOX;
+        if (box_done && box_c0 < p.cols) {
+            fence_proxy_async_smem();                        // generic-proxy writes -> visible to the TMA engine
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(map_out, stage_smem, box_c0, row0);
+                bulk_commit_group();
+            }
         }
     }
 }

@@ -126,6 +126,26 @@ inline int make_tensor_map_u8(CUtensorMap* map, const void* base, uint64_t cols,
     return BM_OK;
 }
 
+// Output matrix [rows x cols] of 2- or 4-byte elements for TMA stores: box = 128 bytes x 32 rows,
+// 128-byte swizzle (matches the staging strips of the epilogue); stores are clipped to the extent.
+inline int make_tensor_map_out(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                               uint64_t pitch_bytes, int elem_size) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail_msg(BM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_size), 32};
+    cuuint32_t elem_strides[2] = {1, 1};
+    CUresult r = fn(map, elem_size == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2,
+                    const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(error_buffer(), 256, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
+        return BM_ERR_CUDA;
+    }
+    return BM_OK;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace bm

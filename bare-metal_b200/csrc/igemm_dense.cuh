@@ -6,8 +6,9 @@
 //   warp 1      MMA issuer    — one lane issues tcgen05.mma.kind::i8 (M=128, N=BN, K=32),
 //                               four per stage; accumulators live in tensor memory, two of
 //                               them, so tile t+1 accumulates while tile t is drained
-//   warps 2..5  epilogue      — tcgen05.ld (each warp its own 32 lanes), fused dequantise
-//                               and cast, vectorised stores
+//   warps 2..9  epilogue      — two warps per tensor-memory lane quarter, each draining half of
+//                               the tile's columns: double-buffered tcgen05.ld, fused
+//                               dequantise and cast, vectorised stores
 //
 // Operand layouts
 //   A        [M x K] row-major (K-major), always
@@ -27,9 +28,10 @@ namespace bm {
 constexpr int kBM = 128;          // tile rows = tensor-memory lanes
 constexpr int kBK = 128;          // K bytes per stage = one 128-byte swizzle span
 constexpr int kUmmaK = 32;        // K per tcgen05.mma for 8-bit operands
-constexpr int kDenseThreads = 192;
+constexpr int kEpiWarps = 8;            // two per tensor-memory lane quarter
+constexpr int kDenseThreads = 64 + 32 * kEpiWarps;
 constexpr int kABytes = kBM * kBK;               // 16 KiB
-constexpr int kSmemBudget = 196608;              // operand ring budget
+constexpr int kSmemBudget = 160 * 1024;          // operand ring budget (the rest: store staging, strips)
 
 template <int BN>
 struct DenseCfg {
@@ -39,22 +41,26 @@ struct DenseCfg {
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int TMEM_COLS_RAW = 2 * BN;
     static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;   // 64..512: powers of two
-    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] drain[1], then tmem slot + abort flag
-    static constexpr int SMEM_BYTES = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16 + 1024 /*alignment slack*/;
+    static constexpr int STORE_OFFSET = STAGES * STAGE_BYTES;     // per-warp TMA-store staging, 1 KiB aligned
+    static constexpr int BAR_OFFSET = STORE_OFFSET + kEpiWarps * kStoreBoxBytes;
+    // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] drain[1], then tmem slot + abort flag,
+    // then one strip of column-side epilogue parameters per epilogue warp
+    static constexpr int NC = BN / 2;                              // columns drained per epilogue warp
+    static constexpr int STRIP_OFFSET = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16;
+    static constexpr int SMEM_BYTES = STRIP_OFFSET + kEpiWarps * (int)sizeof(EpiStrip<NC>) + 1024 /*alignment slack*/;
 };
 
 struct DenseParams {
     EpilogueParams epi;
     int tiles_m, tiles_n, k_blocks;
     int* status;
-    int dbg_lbo, dbg_sbo;      // bring-up only: override the MN-major descriptor offsets when non-zero
+    unsigned long long* dbg_buf;   // bring-up only: per-CTA stall cycle counters (8 per CTA) when non-null
 };
 
 template <int BN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const DenseParams p) {
+                   const __grid_constant__ CUtensorMap map_out, const DenseParams p) {
     using Cfg = DenseCfg<BN>;
     static_assert(!B_MN || BN % 128 == 0, "MN-major B is loaded in 128-column boxes");
     extern __shared__ uint8_t smem_raw[];
@@ -77,6 +83,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n;
+    constexpr uint32_t nstages = Cfg::STAGES;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -85,7 +92,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full_bar(a), 1);
-            mbar_init(acc_empty_bar(a), 4);      // one arrival per epilogue warp
+            mbar_init(acc_empty_bar(a), kEpiWarps);   // one arrival per epilogue warp
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -107,12 +114,15 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             prefetch_tensormap(&map_b);
             uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
             bool ok = true;
+            long long t_wait = 0, t_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 const int m0 = (tile % p.tiles_m) * kBM;
                 const int n0 = (tile / p.tiles_m) * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    const long long tw = clock64();
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
+                    t_wait += clock64() - tw;
                     const uint32_t bar = full_bar(stage);
                     mbar_expect_tx(bar, Cfg::STAGE_BYTES);
                     tma_load_2d(a_smem0 + stage * kABytes, &map_a, bar, kb * kBK, m0);
@@ -126,7 +136,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                     issued |= 1u << stage;
                     issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
-                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                    if (++stage == nstages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) {
@@ -138,6 +148,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                global_timer_ns() - t0 < 20000000ull) {}
                     }
             }
+            if (p.dbg_buf) { p.dbg_buf[blockIdx.x * 8 + 0] = t_wait; p.dbg_buf[blockIdx.x * 8 + 1] = clock64() - t_begin; }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -145,16 +156,21 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             constexpr uint32_t idesc = make_idesc_i8(kBM, BN, B_MN, false);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
+            long long t_full = 0, t_acc = 0, t_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const long long ta = clock64();
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
+                t_acc += clock64() - ta;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    const long long tf = clock64();
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
                         break;
                     }
+                    t_full += clock64() - tf;
                     tc_fence_after_sync();
                     const uint32_t a_addr = a_smem0 + stage * kABytes;
                     const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
@@ -168,16 +184,15 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             // MN-major, 128B swizzle: 128 N-bytes contiguous, 8 K-rows per 1 KiB atom
                             // (stride-dimension offset), next 128-column block one box (16 KiB) on
                             // (leading-dimension offset); a K step of 32 rows is 4 KiB.
-                            b_desc = make_smem_desc(b_addr + ks * (kUmmaK * 128),
-                                                    p.dbg_lbo ? p.dbg_lbo : 128 * kBK,
-                                                    p.dbg_sbo ? p.dbg_sbo : 1024, SWIZZLE_128B_DESC);
+                            b_desc = make_smem_desc(b_addr + ks * (kUmmaK * 128), 128 * kBK, 1024,
+                                                    SWIZZLE_128B_DESC);
                         } else {
                             b_desc = make_smem_desc(b_addr + ks * kUmmaK, 0, 1024, SWIZZLE_128B_DESC);
                         }
                         mma_i8(d_tmem, a_desc, b_desc, idesc, (kb | ks) != 0 ? 1u : 0u);
                     }
                     tc_commit(empty_bar(stage));            // frees the stage when these MMAs retire
-                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                    if (++stage == nstages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 tc_commit(acc_full_bar(acc));               // accumulator complete
@@ -190,32 +205,50 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 uint64_t t0 = global_timer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < 20000000ull) {}
             }
+            if (p.dbg_buf) {
+                p.dbg_buf[blockIdx.x * 8 + 2] = t_full; p.dbg_buf[blockIdx.x * 8 + 3] = t_acc;
+                p.dbg_buf[blockIdx.x * 8 + 4] = clock64() - t_begin;
+            }
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;                        // tensor-memory lanes 32q .. 32q+31
+        const int half = (warp - 2) >> 2;                    // which half of the tile's columns
+        EpiStrip<Cfg::NC>* strip =
+            reinterpret_cast<EpiStrip<Cfg::NC>*>(smem_gen + Cfg::STRIP_OFFSET) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
+        long long t_epi_wait = 0, t_epi_begin = clock64();
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int m0 = (tile % p.tiles_m) * kBM;
-            const int n0 = (tile / p.tiles_m) * BN;
+            const int n0 = (tile / p.tiles_m) * BN + half * Cfg::NC;
+            const int row = m0 + quarter * 32 + lane;
+            // column-side parameters of this tile, fetched while its MMAs are still running
+            stage_strip<EPI, Cfg::NC, false>(p.epi, strip, n0, lane);
+            const float lane_s = lane_scale_of<EPI, false>(p.epi, row);
+            const long long te = clock64();
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
+            t_epi_wait += clock64() - te;
             tc_fence_after_sync();
-            const int row = m0 + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                if (n0 + c * 32 >= p.epi.cols) break;         // warp-uniform
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + c * 32, r);
-                tmem_ld_wait();
-                store_row_chunk<EPI>(p.epi, row, n0 + c * 32, r);
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * Cfg::NC;
+            bool stored = false;
+            if constexpr (Cfg::NC * sizeof(typename OutType<EPI>::type) >= 128) {
+                if (p.epi.tma_ok) {
+                    drain_accumulator_tma<EPI, Cfg::NC>(p.epi, &map_out, taddr, m0 + quarter * 32, lane, n0, strip, lane_s,
+                                                        smem_base + Cfg::STORE_OFFSET + (warp - 2) * kStoreBoxBytes);
+                    stored = true;
+                }
             }
+            if (!stored) drain_accumulator<EPI, Cfg::NC, false>(p.epi, taddr, row, n0, p.epi.cols, strip, lane_s);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
+        }
+        if (lane == 0) bulk_wait_all();                      // TMA stores of this warp have landed
+        if (p.dbg_buf && threadIdx.x == 64) {
+            p.dbg_buf[blockIdx.x * 8 + 5] = t_epi_wait; p.dbg_buf[blockIdx.x * 8 + 6] = clock64() - t_epi_begin;
         }
     }
 

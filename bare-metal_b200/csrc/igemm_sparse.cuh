@@ -32,7 +32,6 @@ namespace bm {
 
 constexpr int kSpKLogical = 256;                 // logical K per stage
 constexpr int kSpMetaBytes = 4096;               // metadata bytes per (128-row block, k-block)
-constexpr int kSpThreads = 192;
 constexpr int kSpSmemBudget = 216 * 1024;
 
 template <int BN>
@@ -49,7 +48,11 @@ struct SparseCfg {
     static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
                                    : COLS_NEEDED <= 256 ? 256 : 512;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int SMEM_BYTES = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16 + 1024;
+    static constexpr int EPI_WARPS = BN >= 64 ? 8 : 4;            // two per lane quarter for wide tiles
+    static constexpr int NC = BN >= 64 ? BN / 2 : 32;             // accumulator columns drained per warp
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int STRIP_OFFSET = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16;
+    static constexpr int SMEM_BYTES = STRIP_OFFSET + EPI_WARPS * (int)sizeof(EpiStrip<NC>) + 1024;
     static_assert(STAGES >= 2, "tile too large for the shared-memory ring");
     static_assert(COLS_NEEDED <= 512, "tensor memory over-subscribed");
 };
@@ -62,7 +65,7 @@ struct SparseParams {
 };
 
 template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI>
-__global__ void __launch_bounds__(kSpThreads, 1)
+__global__ void __launch_bounds__(SparseCfg<BN>::THREADS, 1)
 igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_d,
                     const SparseParams p) {
     using Cfg = SparseCfg<BN>;
@@ -96,7 +99,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full_bar(a), 1);
-            mbar_init(acc_empty_bar(a), 4);
+            mbar_init(acc_empty_bar(a), Cfg::EPI_WARPS);
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -210,41 +213,23 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                     // 0 unless the tile is drained by 8 warps
+        EpiStrip<Cfg::NC>* strip = reinterpret_cast<EpiStrip<Cfg::NC>*>(smem_gen + Cfg::STRIP_OFFSET) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int r0 = (tile % p.tiles_r) * kBM;
-            const int c0 = (tile / p.tiles_r) * BN;
+            const int c0 = (tile / p.tiles_r) * BN + half * Cfg::NC;
+            const int lane_coord = r0 + quarter * 32 + lane;      // row of the sparse operand
+            // never write past this tile's own columns when the tile is narrower than a 32-column chunk
+            int c_limit = TRANSPOSED ? p.epi.rows : p.epi.cols;
+            if (BN < 32 && c_limit > c0 + BN) c_limit = c0 + BN;
+            stage_strip<EPI, Cfg::NC, TRANSPOSED>(p.epi, strip, c0, lane);
+            const float lane_s = lane_scale_of<EPI, TRANSPOSED>(p.epi, lane_coord);
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
             tc_fence_after_sync();
-            const int lane_coord = r0 + quarter * 32 + lane;      // row of the sparse operand
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-            const int c_limit = TRANSPOSED ? p.epi.rows : p.epi.cols;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32 || (BN < 32 && c == 0); ++c) {
-                if (c0 + c * 32 >= c_limit) break;
-                uint32_t r[32];
-                if constexpr (BN >= 32) {
-                    tmem_ld_32x32(taddr + c * 32, r);
-                } else {
-                    // BN = 16: two 8-column loads, the rest of the chunk is masked off below
-                    uint32_t lo[8], hi[8];
-                    tmem_ld_32x8(taddr, lo);
-                    tmem_ld_32x8(taddr + 8, hi);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) { r[j] = lo[j]; r[8 + j] = hi[j]; }
-#pragma unroll
-                    for (int j = 16; j < 32; ++j) r[j] = 0;
-                }
-                tmem_ld_wait();
-                if constexpr (TRANSPOSED) {
-                    EpilogueParams e = p.epi;
-                    if (BN < 32 && e.rows > c0 + BN) e.rows = c0 + BN;   // never write past this tile's tokens
-                    store_col_chunk<EPI>(e, lane_coord, c0 + c * 32, r);
-                } else {
-                    store_row_chunk<EPI>(p.epi, lane_coord, c0 + c * 32, r);
-                }
-            }
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * Cfg::NC;
+            drain_accumulator<EPI, Cfg::NC, TRANSPOSED>(p.epi, taddr, lane_coord, c0, c_limit, strip, lane_s);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
