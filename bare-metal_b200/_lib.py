@@ -26,6 +26,7 @@ SIGNATURES = {
     "bm_sp_meta_tiled_bytes": (_sz, [_i, _i]),
     "bm_sp_pack_meta": (_i, [_p, _i, _p, _i, _i, _p]),
     "bm_igemm_sparse_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _p]),
+    "bm_igemm_sparse_f32_noalloc": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _p]),
     "bm_igemm_sparse_i32": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
     "bm_w8a8_sparse_i32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i64, _p]),
     "bm_w8a8_sparse_f16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i64, _p]),

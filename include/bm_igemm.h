@@ -105,6 +105,18 @@ int bm_sp_pack_meta(const void *meta_in, int meta_format, void *meta_tiled, int 
 int bm_igemm_sparse_f32(const int8_t *A_comp, const int8_t *B, float *C, const uint32_t *meta,
                         int M, int N, int K, float scale_a, float scale_b, void *stream);
 
+/* No counterpart in the reference.  Same arguments and result as bm_igemm_sparse_f32, for callers
+ * that must not allocate device memory (a serving loop with a fixed memory footprint, a process
+ * whose pool owns the whole device, start-up-only allocation policies): the re-tiled metadata
+ * lives in a fixed 2 MiB array inside the library instead of cudaMalloc'ed scratch, and no CUDA
+ * allocation or free is ever made.  Limits: ceil(M/128) * ceil(K/256) * 4096 bytes <= 2 MiB
+ * (M = K = 4096 fits), otherwise BM_ERR_TOO_LARGE and nothing is launched; N % 16 == 0.  All
+ * calls on a device share the array: calls that overlap on the GPU race, so keep them on one
+ * stream or order them.  The first call on each device resolves the array's device address;
+ * make it with that device current and outside stream capture. */
+int bm_igemm_sparse_f32_noalloc(const int8_t *A_comp, const int8_t *B, float *C, const uint32_t *meta,
+                                int M, int N, int K, float scale_a, float scale_b, void *stream);
+
 /* Sparse-left, int32 out, any metadata format, either layout of the dense operand. */
 int bm_igemm_sparse_i32(const int8_t *A_comp, const void *meta, int meta_format, const int8_t *B,
                         int32_t *C, int M, int N, int K, int64_t ldc, int b_layout, void *stream);
