@@ -30,6 +30,10 @@ SIGNATURES = {
     "bm_igemm_sparse_i32": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
     "bm_w8a8_sparse_i32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i64, _p]),
     "bm_w8a8_sparse_f16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i64, _p]),
+    "bm_sp_packed_weight_bytes": (_sz, [_i, _i]),
+    "bm_sp_pack_weights": (_i, [_p, _p, _i, _p, _i, _i, _p]),
+    "bm_w8a8_sparse_i32_packed": (_i, [_p, _p, _p, _i, _i, _i, _i64, _p]),
+    "bm_w8a8_sparse_f16_packed": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i64, _p]),
     "bm_last_device_status": (_i, [C.POINTER(_i)]),
     "bm_last_error_string": (C.c_char_p, []),
     "bm_shutdown": (None, []),

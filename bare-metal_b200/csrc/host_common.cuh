@@ -43,6 +43,10 @@ struct DeviceState {
     int* status = nullptr;          // device int: first bounded-wait failure code, 0 = none
     void* scratch = nullptr;        // library-owned staging (tiled metadata for reference-format calls)
     size_t scratch_bytes = 0;
+    void* sk_workspace = nullptr;   // split-K partial sums (stream-K launches)
+    size_t sk_workspace_bytes = 0;
+    int* sk_counters = nullptr;     // split-K arrival counters, kept at zero between launches
+    size_t sk_counter_ints = 0;
 };
 
 inline std::mutex& state_mutex() {
@@ -83,6 +87,33 @@ inline int ensure_scratch(DeviceState* s, size_t bytes) {
     }
     BM_CUDA_TRY(cudaMalloc(&s->scratch, bytes));
     s->scratch_bytes = bytes;
+    return BM_OK;
+}
+
+// grow-only split-K buffers of the current device (counters are zero-filled when (re)allocated)
+inline int ensure_split_k(DeviceState* s, size_t workspace_bytes, size_t counter_ints) {
+    std::lock_guard<std::mutex> lock(state_mutex());
+    if (s->sk_workspace_bytes < workspace_bytes) {
+        if (s->sk_workspace) {
+            BM_CUDA_TRY(cudaDeviceSynchronize());
+            BM_CUDA_TRY(cudaFree(s->sk_workspace));
+            s->sk_workspace = nullptr;
+            s->sk_workspace_bytes = 0;
+        }
+        BM_CUDA_TRY(cudaMalloc(&s->sk_workspace, workspace_bytes));
+        s->sk_workspace_bytes = workspace_bytes;
+    }
+    if (s->sk_counter_ints < counter_ints) {
+        if (s->sk_counters) {
+            BM_CUDA_TRY(cudaDeviceSynchronize());
+            BM_CUDA_TRY(cudaFree(s->sk_counters));
+            s->sk_counters = nullptr;
+            s->sk_counter_ints = 0;
+        }
+        BM_CUDA_TRY(cudaMalloc(&s->sk_counters, counter_ints * sizeof(int)));
+        BM_CUDA_TRY(cudaMemset(s->sk_counters, 0, counter_ints * sizeof(int)));
+        s->sk_counter_ints = counter_ints;
+    }
     return BM_OK;
 }
 

@@ -57,14 +57,63 @@ struct SparseCfg {
     static_assert(COLS_NEEDED <= 512, "tensor memory over-subscribed");
 };
 
+constexpr int kSpPackedBlock = 16384 + kSpMetaBytes;   // packed weights: swizzled values + metadata per block
+
 struct SparseParams {
     EpilogueParams epi;
-    const uint8_t* meta_tiled;
+    const uint8_t* meta_tiled;         // tiled metadata, or the packed weight blocks when PACKED
     int tiles_r, tiles_c, k_blocks;    // row blocks of the sparse operand, column tiles of the dense one
     int* status;
+    // stream-K (decode shapes): the (tile, k-block) units are dealt out evenly to the CTAs, so a tile
+    // may be shared by several CTAs; partial sums meet in `sk_workspace`, the part that arrives last
+    // (per epilogue warp, counted in `sk_counters`) adds them up and runs the epilogue.  No CTA waits.
+    int stream_k;
+    int* sk_counters;                  // [tiles][epilogue warps], zero between launches (self-resetting)
+    int32_t* sk_workspace;             // [CTAs][2: head / tail share][epilogue warps][NC x 32]
 };
 
-template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI>
+// One contiguous piece of work: k-blocks [kb0, kb1) of one tile.
+struct WorkSegment {
+    int tile, kb0, kb1;
+};
+
+// Deals work to CTA `cta` of `ctas`.  Static mode: whole tiles cta, cta+ctas, ...  Stream-K mode: the
+// units [cta*U/ctas, (cta+1)*U/ctas) of the U = tiles*k_blocks (tile-major) units, cut at tile borders.
+struct WorkIter {
+    long long u, u_end;
+    int tile, tiles, k_blocks, step;
+    bool stream_k;
+    __device__ WorkIter(bool sk, int cta, int ctas, int tiles_, int k_blocks_)
+        : tile(cta), tiles(tiles_), k_blocks(k_blocks_), step(ctas), stream_k(sk) {
+        const long long U = static_cast<long long>(tiles_) * k_blocks_;
+        u = U * cta / ctas;
+        u_end = U * (cta + 1) / ctas;
+    }
+    __device__ bool next(WorkSegment& s) {
+        if (stream_k) {
+            if (u >= u_end) return false;
+            s.tile = static_cast<int>(u / k_blocks);
+            s.kb0 = static_cast<int>(u % k_blocks);
+            const long long left = u_end - u;
+            s.kb1 = (s.kb0 + left < k_blocks) ? static_cast<int>(s.kb0 + left) : k_blocks;
+            u += s.kb1 - s.kb0;
+            return true;
+        }
+        if (tile >= tiles) return false;
+        s.tile = tile;
+        s.kb0 = 0;
+        s.kb1 = k_blocks;
+        tile += step;
+        return true;
+    }
+};
+
+// CTA that owns unit `u` under the stream-K split: the largest i with floor(i*U/ctas) <= u.
+__device__ __forceinline__ int stream_k_owner(long long u, long long U, int ctas) {
+    return static_cast<int>(((u + 1) * ctas - 1) / U);
+}
+
+template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false>
 __global__ void __launch_bounds__(SparseCfg<BN>::THREADS, 1)
 igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_d,
                     const SparseParams p) {
@@ -117,21 +166,28 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
-            prefetch_tensormap(&map_s);
+            if constexpr (!PACKED) prefetch_tensormap(&map_s);
             prefetch_tensormap(&map_d);
             uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int rb = tile % p.tiles_r;
+            WorkIter work(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, p.k_blocks);
+            WorkSegment seg;
+            while (ok && work.next(seg)) {
+                const int rb = seg.tile % p.tiles_r;
                 const int r0 = rb * kBM;
-                const int c0 = (tile / p.tiles_r) * BN;
-                const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) * p.k_blocks * kSpMetaBytes;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                const int c0 = (seg.tile / p.tiles_r) * BN;
+                const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) * p.k_blocks *
+                                                             (PACKED ? kSpPackedBlock : kSpMetaBytes);
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
                     const uint32_t bar = full_bar(stage);
                     mbar_expect_tx(bar, Cfg::STAGE_BYTES);
-                    tma_load_2d(a_smem0 + stage * Cfg::A_BYTES, &map_s, bar, kb * 128, r0);
+                    if constexpr (PACKED)      // pre-swizzled values: one linear 16 KiB copy
+                        bulk_load(a_smem0 + stage * Cfg::A_BYTES, meta_row + static_cast<size_t>(kb) * kSpPackedBlock,
+                                  Cfg::A_BYTES, bar);
+                    else
+                        tma_load_2d(a_smem0 + stage * Cfg::A_BYTES, &map_s, bar, kb * 128, r0);
                     const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
                     if constexpr (DENSE_MN) {
 #pragma unroll
@@ -143,8 +199,12 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                         for (int j = 0; j < 2; ++j)          // [BN rows x 128 K bytes] per box
                             tma_load_2d(b_addr + j * (BN * 128), &map_d, bar, kb * kSpKLogical + j * 128, c0);
                     }
-                    bulk_load(e_smem0 + stage * kSpMetaBytes, meta_row + static_cast<size_t>(kb) * kSpMetaBytes,
-                              kSpMetaBytes, bar);
+                    if constexpr (PACKED)
+                        bulk_load(e_smem0 + stage * kSpMetaBytes,
+                                  meta_row + static_cast<size_t>(kb) * kSpPackedBlock + Cfg::A_BYTES, kSpMetaBytes, bar);
+                    else
+                        bulk_load(e_smem0 + stage * kSpMetaBytes, meta_row + static_cast<size_t>(kb) * kSpMetaBytes,
+                                  kSpMetaBytes, bar);
                     issued |= 1u << stage;
                     issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -165,12 +225,14 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             constexpr uint32_t idesc = make_idesc_i8(kBM, BN, DENSE_MN, true);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            WorkIter work(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, p.k_blocks);
+            WorkSegment seg;
+            while (ok && work.next(seg)) {
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
                         break;
@@ -195,7 +257,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                             b_desc = make_smem_desc(b_addr + (ks >> 1) * (BN * 128) + (ks & 1) * 64, 0, 1024,
                                                     SWIZZLE_128B_DESC);
                         }
-                        mma_i8_sp(d_tmem, a_desc, b_desc, e_tmem + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                        mma_i8_sp(d_tmem, a_desc, b_desc, e_tmem + 2 * ks, idesc, (kb != seg.kb0 || ks != 0) ? 1u : 0u);
                     }
                     tc_commit(empty_bar(stage));
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -216,23 +278,61 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
         const int half = (warp - 2) >> 2;                     // 0 unless the tile is drained by 8 warps
         EpiStrip<Cfg::NC>* strip = reinterpret_cast<EpiStrip<Cfg::NC>*>(smem_gen + Cfg::STRIP_OFFSET) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int r0 = (tile % p.tiles_r) * kBM;
-            const int c0 = (tile / p.tiles_r) * BN + half * Cfg::NC;
+        WorkIter work(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, p.k_blocks);
+        WorkSegment seg;
+        while (work.next(seg)) {
+            const int r0 = (seg.tile % p.tiles_r) * kBM;
+            const int c0 = (seg.tile / p.tiles_r) * BN + half * Cfg::NC;
             const int lane_coord = r0 + quarter * 32 + lane;      // row of the sparse operand
             // never write past this tile's own columns when the tile is narrower than a 32-column chunk
             int c_limit = TRANSPOSED ? p.epi.rows : p.epi.cols;
             if (BN < 32 && c_limit > c0 + BN) c_limit = c0 + BN;
+            const bool whole = (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
             stage_strip<EPI, Cfg::NC, TRANSPOSED>(p.epi, strip, c0, lane);
             const float lane_s = lane_scale_of<EPI, TRANSPOSED>(p.epi, lane_coord);
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * Cfg::NC;
-            drain_accumulator<EPI, Cfg::NC, TRANSPOSED>(p.epi, taddr, lane_coord, c0, c_limit, strip, lane_s);
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if (whole) {
+                drain_accumulator<EPI, Cfg::NC, TRANSPOSED>(p.epi, taddr, lane_coord, c0, c_limit, strip, lane_s);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            } else {
+                // a share of a tile: park the raw sums, then see whether this warp's slice is complete
+                // A CTA's range holds at most two shares: the tail of the tile its range starts in
+                // ("head" slot 0) and the head of the tile it ends in (slot 1).
+                const long long U = static_cast<long long>(num_tiles) * p.k_blocks;
+                const int G = static_cast<int>(gridDim.x);
+                const long long u_first = static_cast<long long>(seg.tile) * p.k_blocks;
+                const int cta_first = stream_k_owner(u_first, U, G);
+                const int parts = stream_k_owner(u_first + p.k_blocks - 1, U, G) - cta_first + 1;
+                constexpr int SLICE = Cfg::NC * 32;
+                auto share_of = [&](int cta) -> int32_t* {
+                    const int which = (static_cast<int>((U * cta / G) / p.k_blocks) == seg.tile) ? 0 : 1;
+                    return p.sk_workspace +
+                           ((static_cast<size_t>(cta) * 2 + which) * Cfg::EPI_WARPS + (warp - 2)) * SLICE;
+                };
+                park_accumulator<Cfg::NC>(taddr, share_of(static_cast<int>(blockIdx.x)), lane);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(acc));        // tensor memory is free again
+                __threadfence();
+                int last = 0;
+                int* counter = p.sk_counters + seg.tile * Cfg::EPI_WARPS + (warp - 2);
+                if (lane == 0) {
+                    last = (atomicAdd(counter, 1) == parts - 1);
+                    if (last) *counter = 0;                            // ready for the next launch
+                }
+                last = __shfl_sync(0xFFFFFFFFu, last, 0);
+                if (last) {
+                    __threadfence();
+                    finish_parked<EPI, Cfg::NC, TRANSPOSED>(
+                        p.epi, [&](int part) -> const int32_t* { return share_of(cta_first + part); }, parts,
+                        lane_coord, c0, c_limit, strip, lane_s, lane);
+                }
+            }
             if (++acc == Cfg::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
         }
     }

@@ -24,9 +24,17 @@ __device__ __forceinline__ void tiled_coords(size_t unit, int k_blocks, int& row
     k_byte0 = (kb * 2 + j) * 16;                    // first metadata byte of this row's 16
 }
 
+// Where unit u of the tiled metadata goes: blocks of 4 KiB (256 units) that are either packed back
+// to back (block_stride = 4096, block_offset = 0) or embedded in the 20 KiB blocks of the packed
+// weight format (block_stride = 20480, block_offset = 16384).
+__device__ __forceinline__ size_t meta_unit_offset(size_t unit, size_t block_stride, size_t block_offset) {
+    return (unit >> 8) * block_stride + block_offset + (unit & 255) * 16;
+}
+
 // per-row nibble bytes [R x K/8] -> tiled; one thread per 16-byte unit
 __global__ void pack_meta_rows_kernel(const uint8_t* __restrict__ rows_meta, uint8_t* __restrict__ tiled,
-                                      int R, int K, int k_blocks, size_t units) {
+                                      int R, int K, int k_blocks, size_t units,
+                                      size_t block_stride, size_t block_offset) {
     const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (unit >= units) return;
     int row, b0;
@@ -40,12 +48,14 @@ __global__ void pack_meta_rows_kernel(const uint8_t* __restrict__ rows_meta, uin
                    ? *reinterpret_cast<const uint32_t*>(rows_meta + static_cast<size_t>(row) * row_bytes + b)
                    : 0x44444444u;
     }
-    *reinterpret_cast<uint4*>(tiled + unit * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, block_stride, block_offset)) =
+        make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // reference uint32 words -> tiled; one thread per 16-byte unit (4 K steps of 32)
 __global__ void pack_meta_ref_kernel(const uint32_t* __restrict__ meta_ref, uint8_t* __restrict__ tiled,
-                                     int R, int K, int k_blocks, size_t units) {
+                                     int R, int K, int k_blocks, size_t units,
+                                     size_t block_stride, size_t block_offset) {
     const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (unit >= units) return;
     int row, b0;
@@ -59,7 +69,40 @@ __global__ void pack_meta_ref_kernel(const uint32_t* __restrict__ meta_ref, uint
                    ? meta_ref[(static_cast<size_t>(row / 16) * k_steps + s) * 8 + (row % 16) % 8]
                    : 0x44444444u;
     }
-    *reinterpret_cast<uint4*>(tiled + unit * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, block_stride, block_offset)) =
+        make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// tiled metadata (4 KiB blocks) -> the metadata part of packed weight blocks
+__global__ void pack_meta_copy_kernel(const uint8_t* __restrict__ tiled_in, uint8_t* __restrict__ packed,
+                                      size_t units, size_t block_stride, size_t block_offset) {
+    const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (unit >= units) return;
+    *reinterpret_cast<uint4*>(packed + meta_unit_offset(unit, block_stride, block_offset)) =
+        *reinterpret_cast<const uint4*>(tiled_in + unit * 16);
+}
+
+// Compressed 2:4 values comp[R x K/2] -> packed weight blocks.  Block (rb, kb) holds rows
+// [128 rb, +128) x compressed bytes [128 kb, +128) as 128 rows x 128 B laid out exactly as a TMA load
+// with 128-byte swizzle would leave them in shared memory (16-byte chunk c of row r sits at
+// r*128 + ((c ^ (r & 7)) << 4)), so the GEMM can fetch the whole 16 KiB with one linear bulk copy.
+// Rows / bytes beyond the operand are zero.  One thread per 16-byte chunk.
+__global__ void pack_comp_blocks_kernel(const int8_t* __restrict__ comp, uint8_t* __restrict__ packed,
+                                        int R, int K, int k_blocks, size_t chunks, size_t block_stride) {
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= chunks) return;
+    const int c = static_cast<int>(idx & 7);
+    const int r = static_cast<int>((idx >> 3) & 127);
+    const size_t blk = idx >> 10;
+    const int kb = static_cast<int>(blk % k_blocks);
+    const int rb = static_cast<int>(blk / k_blocks);
+    const int row = rb * 128 + r;
+    const int byte0 = kb * 128 + c * 16;
+    const int row_bytes = K / 2;                   // K % 32 == 0, so rows are whole 16-byte chunks
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < R && byte0 < row_bytes)
+        v = *reinterpret_cast<const uint4*>(comp + static_cast<size_t>(row) * row_bytes + byte0);
+    *reinterpret_cast<uint4*>(packed + blk * block_stride + r * 128 + ((c ^ (r & 7)) << 4)) = v;
 }
 
 // B[K x N] -> W[N x K], 64 x 64 byte tiles through shared memory

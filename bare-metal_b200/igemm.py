@@ -175,6 +175,35 @@ def w8a8_sparse_linear(X, W_comp, W_meta_tiled, D, sa, sw, M, N, K, ldd=None):
     return D
 
 
+def sp_pack_weights(W_comp, W_meta, meta_format, N, K):
+    """One-time repack of 2:4 sparse weights (values + positions) into contiguous 20 KiB blocks."""
+    L = _lib.load()
+    packed = torch.empty(L.bm_sp_packed_weight_bytes(N, K), dtype=torch.uint8, device=W_comp.device)
+    _lib.check(L.bm_sp_pack_weights(_dev(W_comp, torch.int8, "W_comp"), W_meta.data_ptr(), meta_format,
+                                    packed.data_ptr(), N, K, _stream()), "bm_sp_pack_weights")
+    return packed
+
+
+def w8a8_sparse_i32_packed(X, W_packed, C, M, N, K):
+    L = _lib.load()
+    rc = L.bm_w8a8_sparse_i32_packed(_dev(X, torch.int8, "X"), _dev(W_packed, torch.uint8, "W_packed"),
+                                     _out(C, torch.int32, "C"), M, N, K, C.stride(0) if C.dim() == 2 else N, _stream())
+    _lib.check(rc, "bm_w8a8_sparse_i32_packed")
+    return C
+
+
+def w8a8_sparse_linear_packed(X, W_packed, D, sa, sw, M, N, K, ldd=None):
+    L = _lib.load()
+    _check_f16(D)
+    if ldd is None:
+        ldd = D.stride(0) if D.dim() == 2 else N
+    rc = L.bm_w8a8_sparse_f16_packed(_dev(X, torch.int8, "X"), _dev(W_packed, torch.uint8, "W_packed"), D.data_ptr(),
+                                     _dev(sa, torch.float32, "sa"), _dev(sw, torch.float32, "sw"), M, N, K, ldd,
+                                     _stream())
+    _lib.check(rc, "bm_w8a8_sparse_f16_packed")
+    return D
+
+
 def last_device_status() -> int:
     """Status word a bounded in-kernel wait sets when it gives up (0 = none); clears it."""
     import ctypes

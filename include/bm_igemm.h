@@ -129,6 +129,18 @@ int bm_w8a8_sparse_f16(const int8_t *X, const int8_t *W_comp, const void *W_meta
                        const float *sa_m, const float *sw_n, int M, int N, int K, int64_t ldd,
                        void *stream);
 
+/* Packed sparse weights: per (128-row block, 256-wide K block) one contiguous 20 KiB block —
+ * 16 KiB of kept values already in the shared-memory order of the kernel, then 4 KiB of tiled
+ * metadata — so a decode-shaped GEMM streams the weights from HBM strictly sequentially.
+ * One-time repack (no reference counterpart; the reference only compresses, sparse_meta_int8.h:116). */
+size_t bm_sp_packed_weight_bytes(int N, int K);
+int bm_sp_pack_weights(const int8_t *W_comp, const void *W_meta, int meta_format, void *W_packed,
+                       int N, int K, void *stream);
+int bm_w8a8_sparse_i32_packed(const int8_t *X, const void *W_packed, int32_t *C, int M, int N, int K,
+                              int64_t ldc, void *stream);
+int bm_w8a8_sparse_f16_packed(const int8_t *X, const void *W_packed, uint16_t *D, const float *sa_m,
+                              const float *sw_n, int M, int N, int K, int64_t ldd, void *stream);
+
 /* =======================================================================================
  * Library state
  * ===================================================================================== */

@@ -43,3 +43,22 @@ def assert_clean_status():
     from bare_metal_b200 import igemm
     torch.cuda.synchronize()
     assert igemm.last_device_status() == 0, "a bounded device-side wait gave up"
+
+
+@contextmanager
+def env(**kv):
+    """Temporarily set environment variables read by the launchers' testing hooks."""
+    old = {k: os.environ.get(k) for k in kv}
+    for k, v in kv.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = str(v)
+    try:
+        yield
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v

@@ -143,3 +143,69 @@ def test_sparse_repeat_launches_are_bit_identical():
         else:
             assert torch.equal(C, first), f"launch {i} differs"
     assert_clean_status()
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(1, 256, 512, 16), (16, 384, 1024, 16), (64, 200, 288, 64), (128, 256, 512, 128),
+                                      (300, 520, 800, None), (33, 1024, 2048, None)])
+def test_packed_sparse_weights_match_oracle(M, N, K, bn):
+    """Packed weight blocks (pre-swizzled values + metadata, 20 KiB per block): same results."""
+    comp, nib = oracle.gen_sparse_rows(N, K, 2, 31)
+    X = oracle.gen_int8((M, K), 2, 32)
+    want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
+    packed = ig.sp_pack_weights(T(comp), T(nib), ig.BM_META_ROWS, N, K)
+    C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
+    with forced_bn(bn):
+        ig.w8a8_sparse_i32_packed(T(X), packed, C, M, N, K)
+    assert_clean_status()
+    assert np.array_equal(C.cpu().numpy(), want)
+    sa, sw = oracle.gen_scales(M, 2, 3), oracle.gen_scales(N, 2, 4)
+    D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+    with forced_bn(bn):
+        ig.w8a8_sparse_linear_packed(T(X), packed, D, T(sa), T(sw), M, N, K)
+    assert_clean_status()
+    assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)) <= 1
+    # packing from already-tiled metadata gives the same blocks
+    tiled = ig.sp_pack_meta(T(nib), ig.BM_META_ROWS, N, K)
+    packed2 = ig.sp_pack_weights(T(comp), tiled, ig.BM_META_TILED, N, K)
+    assert torch.equal(packed, packed2)
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(1, 384, 2048, 16), (16, 1152, 4096, 16), (64, 640, 1536, 64),
+                                      (40, 200, 800, None), (256, 512, 2048, 128), (8, 28672, 1024, None)])
+def test_stream_k_split_matches_oracle(M, N, K, bn):
+    """K ranges of a tile shared between CTAs (stream-K): partial sums are added exactly, whatever
+    the split; run twice so the self-resetting arrival counters are exercised."""
+    from _gpu import env
+    comp, nib = oracle.gen_sparse_rows(N, K, 3, 41)
+    X = oracle.gen_int8((M, K), 3, 42)
+    want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
+    packed = ig.sp_pack_weights(T(comp), T(nib), ig.BM_META_ROWS, N, K)
+    sa, sw = oracle.gen_scales(M, 3, 3), oracle.gen_scales(N, 3, 4)
+    want16 = oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)
+    with env(BM_STREAM_K=1), forced_bn(bn):
+        for _ in range(2):
+            C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
+            ig.w8a8_sparse_i32_packed(T(X), packed, C, M, N, K)
+            assert_clean_status()
+            assert np.array_equal(C.cpu().numpy(), want)
+            D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+            ig.w8a8_sparse_linear_packed(T(X), packed, D, T(sa), T(sw), M, N, K)
+            assert_clean_status()
+            assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
+    # the static schedule gives the same integers
+    with env(BM_STREAM_K=0), forced_bn(bn):
+        C2 = torch.empty((M, N), dtype=torch.int32, device=dev())
+        ig.w8a8_sparse_i32_packed(T(X), packed, C2, M, N, K)
+        assert np.array_equal(C2.cpu().numpy(), want)
+
+
+def test_stream_k_reference_left_orientation():
+    from _gpu import env
+    M, N, K = 384, 256, 2048
+    dense, comp, meta, B = bench_sparse_inputs(M, N, K)
+    want = oracle.igemm(dense, B, threads=0)
+    with env(BM_STREAM_K=1):
+        C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
+        ig.igemm_sparse_i32(T(comp), T(meta.view(np.int32)), ig.BM_META_REF, T(B), C, M, N, K, ig.BM_B_KN)
+        assert_clean_status()
+    assert np.array_equal(C.cpu().numpy(), want)
