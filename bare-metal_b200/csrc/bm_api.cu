@@ -7,6 +7,7 @@
 #include "igemm_dense.cuh"
 #include "igemm_dense_pair.cuh"
 #include "igemm_sparse.cuh"
+#include "igemm_sparse_pair.cuh"
 #include "pack_kernels.cuh"
 
 namespace bm {
@@ -244,6 +245,40 @@ static int launch_sparse_inst(const CUtensorMap& ms, const CUtensorMap& md, cons
     return BM_OK;
 }
 
+// CTA-pair kernel for sparse weights: 256 channels x 192 tokens per pair
+template <int EPI>
+static int launch_sparse_pair(const CUtensorMap& mw, const CUtensorMap& me, const CUtensorMap& mx, const SparseParams& p,
+                              int pairs, cudaStream_t stream) {
+    auto kern = igemm_sparse_pair_kernel<EPI>;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    BM_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev]) {
+        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSpPairSmemBytes));
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kDenseThreads);
+    cfg.dynamicSmemBytes = kSpPairSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mw, me, mx, p));
+    return BM_OK;
+}
+
+// BM_SPARSE_PAIR=0 keeps large sparse-weight problems on the single-CTA kernel (testing hook)
+static bool sparse_pair_enabled() {
+    const char* e = getenv("BM_SPARSE_PAIR");
+    return !e || atoi(e) != 0;
+}
+
 // mode 0: sparse operand on the left, out[r][c];  mode 1: sparse weights, out[c][r]
 static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* meta_tiled, const int8_t* Dn,
                        void* out, int R, int Cn, int K, long long ld, int dense_layout, float tensor_scale,
@@ -263,6 +298,39 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
 
     const int tiles_r = ceil_div(R, kBM);
     int bn = forced_bn();
+
+    // large token counts with sparse weights: CTA pairs (256 channels x 192 tokens per pair)
+    if (mode == 1 && !dense_mn && !packed && sparse_pair_enabled() && dev->sm_count >= 2 &&
+        (bn == 192 || (bn == 0 && Cn >= 192 && ceil_div(R, 256) * ceil_div(Cn, kSpPairBN) >= dev->sm_count / 2))) {
+        CUtensorMap map_w, map_e, map_x;
+        if (int rc = make_tensor_map_u8(&map_w, S_comp, K / 2, R, K / 2, 128, kBM, true)) return rc;
+        const size_t units = meta_tiled_bytes(R, K) / 16;
+        if (int rc = make_tensor_map_u8(&map_e, meta_tiled, 16, units, 16, 16, 256, false)) return rc;
+        if (int rc = make_tensor_map_u8(&map_x, Dn, K, Cn, K, 128, kSpPairHalfN, true)) return rc;
+        SparseParams p{};
+        p.epi.out = out;
+        p.epi.ld = ld;
+        p.epi.rows = out_rows;
+        p.epi.cols = out_cols;
+        p.epi.tensor_scale = tensor_scale;
+        p.epi.row_scale = row_scale;
+        p.epi.col_scale = col_scale;
+        p.epi.vec_ok = aligned16(out) && (static_cast<size_t>(ld) * out_elem_size(epi)) % 16 == 0;
+        p.meta_tiled = meta_tiled;
+        p.tiles_r = ceil_div(R, 256);
+        p.tiles_c = ceil_div(Cn, kSpPairBN);
+        p.k_blocks = ceil_div(K, kSpKLogical);
+        p.status = dev->status;
+        const int pair_tiles = p.tiles_r * p.tiles_c;
+        const int max_pairs = dev->sm_count / 2;
+        const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+        cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+        if (epi == EPI_I32) return launch_sparse_pair<EPI_I32>(map_w, map_e, map_x, p, pairs, stream);
+        if (epi == EPI_F16_ROWCOL) return launch_sparse_pair<EPI_F16_ROWCOL>(map_w, map_e, map_x, p, pairs, stream);
+        return fail_msg(BM_ERR_LAYOUT, "unsupported epilogue for the sparse pair kernel");
+    }
+    if (bn == 192) bn = 0;
+
     if (bn == 0) {
         if (mode == 1) {
             // tokens on the accumulator columns: the narrowest tile that holds them, up to 128

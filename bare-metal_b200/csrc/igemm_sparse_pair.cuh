@@ -1,0 +1,220 @@
+// igemm_sparse_pair.cuh — 2:4-sparse WEIGHT GEMM on CTA pairs: tcgen05.mma.sp.cta_group::2.
+//
+// D^T = W_sparse * X^T with 256 output channels x 192 tokens per CTA pair.  CTA r of the pair
+// stages, per 256-wide K block: its 128 weight rows (kept values 128 x 128 B, TMA, 128-byte
+// swizzle), their 4 KiB of position metadata (one untiled TMA box of 256 x 16 B) and HALF of the
+// token tile (96 rows x 256 B as two swizzled boxes) — 44 KiB per stage and CTA against 84 KiB for
+// a lone CTA with a 256-token tile.  The leader's MMA lane copies the metadata of BOTH CTAs into
+// tensor memory (tcgen05.cp.cta_group::2) and issues four sparse MMAs (M = 256, N = 192, K = 64
+// logical) per stage.  Accumulators: 2 x 192 columns, metadata 8 columns per stage behind them.
+// Lanes are output channels, accumulator columns are tokens, so the epilogue writes D[m][n] with
+// 32 adjacent channels per warp store.  Barrier protocol as in igemm_dense_pair.cuh; no copy is
+// multicast.
+#pragma once
+#include "epilogue.cuh"
+#include "igemm_dense.cuh"
+#include "igemm_sparse.cuh"
+#include "sm100_ptx.cuh"
+
+namespace bm {
+
+constexpr int kSpPairBN = 192;                       // tokens per pair tile (MMA N)
+constexpr int kSpPairHalfN = kSpPairBN / 2;          // token rows staged per CTA
+constexpr int kSpPairABytes = 128 * 128;             // kept values
+constexpr int kSpPairBBytes = kSpPairHalfN * kSpKLogical;   // 24 KiB
+constexpr int kSpPairStageBytes = kSpPairABytes + kSpMetaBytes + kSpPairBBytes;   // 44 KiB
+constexpr int kSpPairStages = 4;
+constexpr int kSpPairEBase = 2 * kSpPairBN;          // metadata columns start after the accumulators
+constexpr int kSpPairTmemCols = 512;
+constexpr int kSpPairNC = kSpPairBN / 2;             // 96 accumulator columns per epilogue warp
+constexpr int kSpPairBarOffset = kSpPairStages * kSpPairStageBytes;
+constexpr int kSpPairStripOffset = kSpPairBarOffset + (2 * kSpPairStages + 5) * 8 + 16;
+constexpr int kSpPairSmemBytes = kSpPairStripOffset + kEpiWarps * (int)sizeof(EpiStrip<kSpPairNC>) + 1024;
+
+__device__ __forceinline__ void tmem_cp_128x128b_pair(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+__device__ __forceinline__ void mma_i8_sp_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t e_tmem,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.sp.cta_group::2.kind::i8 [%0], %1, %2, [%3], %4, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// map_w: kept values [N x K/2]; map_e: tiled metadata as [units x 16 B]; map_x: tokens [M x K]
+template <int EPI>
+__global__ void __launch_bounds__(kDenseThreads, 1)
+igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_e,
+                         const __grid_constant__ CUtensorMap map_x, const SparseParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t a_smem0 = smem_base;
+    const uint32_t b_smem0 = a_smem0 + kSpPairStages * kSpPairABytes;
+    const uint32_t e_smem0 = b_smem0 + kSpPairStages * kSpPairBBytes;
+    const uint32_t bar0 = smem_base + kSpPairBarOffset;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kSpPairStages + s); };
+    auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * kSpPairStages + a); };
+    auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * kSpPairStages + 2 + a); };
+    const uint32_t drain_bar = bar0 + 8u * (2 * kSpPairStages + 4);
+    const uint32_t tmem_slot = bar0 + 8u * (2 * kSpPairStages + 5);
+    volatile uint32_t* tmem_slot_gen =
+        reinterpret_cast<volatile uint32_t*>(smem_gen + kSpPairBarOffset + 8 * (2 * kSpPairStages + 5));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot_gen + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+    const int num_tiles = p.tiles_r * p.tiles_c;        // tiles of 256 channels x 192 tokens
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kSpPairStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 2 * kEpiWarps);
+        }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, kSpPairTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer (both CTAs)
+        if (lane == 0) {
+            prefetch_tensormap(&map_w);
+            prefetch_tensormap(&map_e);
+            prefetch_tensormap(&map_x);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                const int rb = (tile % p.tiles_r) * 2 + static_cast<int>(rank);       // 128-row block of W
+                const int t0 = (tile / p.tiles_r) * kSpPairBN + static_cast<int>(rank) * kSpPairHalfN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                      DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
+                    const uint32_t leader_full = mapa_shared(full_bar(stage), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kSpPairStageBytes);
+                    tma_load_2d_pair(a_smem0 + stage * kSpPairABytes, &map_w, leader_full, kb * 128, rb * 128);
+                    tma_load_2d_pair(e_smem0 + stage * kSpMetaBytes, &map_e, leader_full, 0,
+                                     (rb * p.k_blocks + kb) * 256);
+                    const uint32_t b_addr = b_smem0 + stage * kSpPairBBytes;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        tma_load_2d_pair(b_addr + j * (kSpPairHalfN * 128), &map_x, leader_full,
+                                         kb * kSpKLogical + j * 128, t0);
+                    if (++stage == kSpPairStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_i8(256, kSpPairBN, false, true);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
+                                  DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kSpPairBN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = a_smem0 + stage * kSpPairABytes;
+                    const uint32_t b_addr = b_smem0 + stage * kSpPairBBytes;
+                    const uint32_t e_addr = e_smem0 + stage * kSpMetaBytes;
+                    const uint32_t e_tmem = tmem_base + kSpPairEBase + stage * 8;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        tmem_cp_128x128b_pair(e_tmem + 4 * j, make_smem_desc(e_addr + j * 2048, 0, 128, SWIZZLE_NONE_DESC));
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t a_desc = make_smem_desc(a_addr + ks * 32, 0, 1024, SWIZZLE_128B_DESC);
+                        const uint64_t b_desc = make_smem_desc(b_addr + (ks >> 1) * (kSpPairHalfN * 128) + (ks & 1) * 64,
+                                                               0, 1024, SWIZZLE_128B_DESC);
+                        mma_i8_sp_pair(d_tmem, a_desc, b_desc, e_tmem + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                    }
+                    tc_commit_pair(empty_bar(stage));
+                    tc_commit_pair(mapa_shared(empty_bar(stage), 1));
+                    if (++stage == kSpPairStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit_pair(acc_full_bar(acc));
+                tc_commit_pair(mapa_shared(acc_full_bar(acc), 1));
+                acc ^= 1u;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+            if (!ok) {
+                tc_commit_pair(drain_bar);
+                uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < 20000000ull) {}
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps (both CTAs)
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        EpiStrip<kSpPairNC>* strip = reinterpret_cast<EpiStrip<kSpPairNC>*>(smem_gen + kSpPairStripOffset) + (warp - 2);
+        uint32_t acc = 0, acc_phase = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+            const int n0 = (tile % p.tiles_r) * 256 + static_cast<int>(rank) * 128;           // first channel of this CTA
+            const int t0 = (tile / p.tiles_r) * kSpPairBN + half * kSpPairNC;                  // first token of this warp
+            const int channel = n0 + quarter * 32 + lane;
+            stage_strip<EPI, kSpPairNC, true>(p.epi, strip, t0, lane);
+            const float lane_s = lane_scale_of<EPI, true>(p.epi, channel);
+            if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
+                break;
+            tc_fence_after_sync();
+            const uint32_t taddr =
+                tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kSpPairBN + half * kSpPairNC;
+            drain_accumulator<EPI, kSpPairNC, true>(p.epi, taddr, channel, t0, p.epi.rows, strip, lane_s);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
+            acc ^= 1u;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) {}
+    }
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, kSpPairTmemCols);
+    }
+}
+
+}  // namespace bm
