@@ -36,7 +36,7 @@ static size_t out_elem_size(int epi) { return epi == EPI_F16_ROWCOL ? 2 : 4; }
 // dense
 // =========================================================================================
 template <int BN, bool B_MN, int EPI>
-static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& mo,
                              const DenseParams& p, int grid, cudaStream_t stream) {
     using Cfg = DenseCfg<BN>;
     auto kern = igemm_dense_kernel<BN, B_MN, EPI>;
@@ -54,7 +54,7 @@ static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const
 
 // CTA-pair kernel: 2-CTA clusters, one pair per two SMs, 256 x 256 tiles
 template <bool B_MN, int EPI>
-static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& mo,
                              const DenseParams& p, int pairs, cudaStream_t stream) {
     auto kern = igemm_dense_pair_kernel<B_MN, EPI>;
     static bool configured[kMaxDevices] = {};
@@ -87,7 +87,7 @@ static bool pair_enabled() {
 }
 
 template <bool B_MN, int EPI>
-static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& mo,
                            const DenseParams& p, int grid, cudaStream_t stream) {
     switch (bn) {
         case 256: return launch_dense_inst<256, B_MN, EPI>(ma, mb, mo, p, grid, stream);
@@ -100,7 +100,7 @@ static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb,
 
 static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M, int N, int K, long long ldc,
                       int b_layout, float tensor_scale, const float* row_scale, const float* col_scale,
-                      const int* col_zero, void* stream_v) {
+                      const int* col_zero, void* stream_v, void* const* peers = nullptr, int n_peers = 0) {
     if (!A || !B) return fail_msg(BM_ERR_NULL, "operand pointer is NULL");
     if (M <= 0 || N <= 0 || K <= 0) return fail_msg(BM_ERR_SHAPE, "M, N, K must be positive");
     if (b_layout != BM_B_KN && b_layout != BM_B_NK) return fail_msg(BM_ERR_LAYOUT, "unknown B layout tag");
@@ -125,6 +125,7 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
         if (N <= bn / 2 && bn / 2 >= min_bn) bn /= 2;
     }
     if (b_mn && bn < 128) bn = 128;
+    if (n_peers > 0 && bn < 128) bn = 128;          // the gather rides on the TMA-store epilogue (tiles >= 128 wide)
 
     const bool use_pair = (bn == 256) && pair_enabled() && dev->sm_count >= 2;
 
@@ -146,9 +147,24 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
     p.epi.col_scale = col_scale;
     p.epi.col_zero = col_zero;
     p.epi.vec_ok = aligned16(C) && (static_cast<size_t>(ldc) * out_elem_size(epi)) % 16 == 0;
-    CUtensorMap map_out{};
-    if (p.epi.vec_ok && !getenv("BM_NO_TMA_STORE")) {
-        if (int rc = make_tensor_map_out(&map_out, C, N, M, static_cast<size_t>(ldc) * out_elem_size(epi),
+    OutMaps map_out{};
+    p.n_out = 1;
+    if (n_peers > 0) {
+        // the same slab goes to every GPU of the group: one tensor map per destination buffer
+        if (n_peers > kMaxOutMaps) return fail_msg(BM_ERR_TOO_LARGE, "at most 8 gather destinations");
+        for (int d = 0; d < n_peers; ++d) {
+            if (!peers[d] || !aligned16(peers[d])) return fail_msg(BM_ERR_ALIGN, "gather destinations must be 16-byte aligned");
+            if (int rc = make_tensor_map_out(&map_out.m[d], peers[d], N, M, static_cast<size_t>(ldc) * out_elem_size(epi),
+                                             static_cast<int>(out_elem_size(epi))))
+                return rc;
+        }
+        if ((static_cast<size_t>(ldc) * out_elem_size(epi)) % 16 != 0)
+            return fail_msg(BM_ERR_ALIGN, "gather needs a 16-byte aligned output pitch");
+        p.n_out = n_peers;
+        p.epi.tma_ok = 1;
+        p.epi.vec_ok = 1;
+    } else if (p.epi.vec_ok && !getenv("BM_NO_TMA_STORE")) {
+        if (int rc = make_tensor_map_out(&map_out.m[0], C, N, M, static_cast<size_t>(ldc) * out_elem_size(epi),
                                          static_cast<int>(out_elem_size(epi))))
             return rc;
         p.epi.tma_ok = 1;
@@ -460,6 +476,13 @@ int bm_igemm_i8_f32_perchannel(const int8_t* A, const int8_t* B, float* C, int M
 int bm_w8a8_f16(const int8_t* X, const int8_t* W, uint16_t* D, const float* sa_m, const float* sw_n, int M, int N,
                 int K, int64_t ldd, int w_layout, void* stream) {
     return dense_gemm(EPI_F16_ROWCOL, X, W, D, M, N, K, ldd, w_layout, 1.f, sa_m, sw_n, nullptr, stream);
+}
+
+int bm_w8a8_f16_gather(const int8_t* X, const int8_t* W, uint16_t* const* D_peers, int n_peers, const float* sa_m,
+                       const float* sw_n, int M, int N, int K, int64_t ldd, int w_layout, void* stream) {
+    if (!D_peers || n_peers <= 0) return fail_msg(BM_ERR_NULL, "no gather destinations given");
+    return dense_gemm(EPI_F16_ROWCOL, X, W, D_peers[0], M, N, K, ldd, w_layout, 1.f, sa_m, sw_n, nullptr, stream,
+                      reinterpret_cast<void* const*>(D_peers), n_peers);
 }
 
 int bm_pack_b_kn_to_nk(const int8_t* B_kn, int8_t* W_nk, int K, int N, void* stream) {

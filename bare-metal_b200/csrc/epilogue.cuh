@@ -238,10 +238,18 @@ __device__ __forceinline__ void finish_parked(const EpilogueParams& p, PartPtr p
 // ------------------------------------------------------------------------------------------------
 constexpr int kStoreBoxBytes = 32 * 128;          // per-warp staging strip
 
+// Up to kMaxOutMaps destinations of one output tile: the local matrix, or the same column slab of
+// the output on every GPU of an N-split group (peer-mapped buffers) — the all-gather of the slab is
+// then nothing but extra TMA stores of the box that is already staged in shared memory.
+constexpr int kMaxOutMaps = 8;
+struct OutMaps {
+    CUtensorMap m[kMaxOutMaps];
+};
+
 template <int EPI, int NC>
-__device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const CUtensorMap* map_out, uint32_t taddr,
-                                                      int row0, int lane, int col0, const EpiStrip<NC>* strip,
-                                                      float lane_s, uint32_t stage_smem) {
+__device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const OutMaps& maps, int n_maps,
+                                                      uint32_t taddr, int row0, int lane, int col0,
+                                                      const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem) {
     using T = typename OutType<EPI>::type;
     static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
     constexpr int CHUNKS = NC / 32;
@@ -289,7 +297,7 @@ __device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, c
             fence_proxy_async_smem();                        // generic-proxy writes -> visible to the TMA engine
             __syncwarp();
             if (lane == 0) {
-                tma_store_2d(map_out, stage_smem, box_c0, row0);
+                for (int d = 0; d < n_maps; ++d) tma_store_2d(&maps.m[d], stage_smem, box_c0, row0);
                 bulk_commit_group();
             }
         }

@@ -54,13 +54,14 @@ struct DenseParams {
     EpilogueParams epi;
     int tiles_m, tiles_n, k_blocks;
     int* status;
+    int n_out;                 // number of output destinations in the OutMaps argument (1 unless gathering)
     unsigned long long* dbg_buf;   // bring-up only: per-CTA stall cycle counters (8 per CTA) when non-null
 };
 
 template <int BN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const __grid_constant__ CUtensorMap map_out, const DenseParams p) {
+                   const __grid_constant__ OutMaps maps_out, const DenseParams p) {
     using Cfg = DenseCfg<BN>;
     static_assert(!B_MN || BN % 128 == 0, "MN-major B is loaded in 128-column boxes");
     extern __shared__ uint8_t smem_raw[];
@@ -234,7 +235,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             bool stored = false;
             if constexpr (Cfg::NC * sizeof(typename OutType<EPI>::type) >= 128) {
                 if (p.epi.tma_ok) {
-                    drain_accumulator_tma<EPI, Cfg::NC>(p.epi, &map_out, taddr, m0 + quarter * 32, lane, n0, strip, lane_s,
+                    drain_accumulator_tma<EPI, Cfg::NC>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip, lane_s,
                                                         smem_base + Cfg::STORE_OFFSET + (warp - 2) * kStoreBoxBytes);
                     stored = true;
                 }

@@ -40,7 +40,7 @@ constexpr int kPairSmemBytes = kPairStripOffset + kEpiWarps * (int)sizeof(EpiStr
 template <bool B_MN, int EPI>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const __grid_constant__ CUtensorMap map_out, const DenseParams p) {
+                        const __grid_constant__ OutMaps maps_out, const DenseParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -191,7 +191,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t taddr =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN + half * kPairNC;
             if (p.epi.tma_ok)
-                drain_accumulator_tma<EPI, kPairNC>(p.epi, &map_out, taddr, m0 + quarter * 32, lane, n0, strip, lane_s,
+                drain_accumulator_tma<EPI, kPairNC>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip, lane_s,
                                                     smem_base + kPairStoreOffset + (warp - 2) * kStoreBoxBytes);
             else
                 drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, p.epi.cols, strip, lane_s);

@@ -159,6 +159,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the sparse / decode side measurements")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: fused = GEMM epilogue stores to all ranks over NVLink; nccl = GEMM then all-gather")
     ap.add_argument("--profile", action="store_true",
                     help="profiler-friendly run: only warm-up + the timed steps of the headline kernel")
     args = ap.parse_args()
@@ -200,20 +202,25 @@ def main() -> None:
     A_d = [torch.from_numpy(A_h).to(devn) for _ in range(n_sets)]
     W_d = [torch.from_numpy(W_h).to(devn) for _ in range(n_sets)]
     sa_d, sw_d = torch.from_numpy(sa_h).to(devn), torch.from_numpy(sw_h).to(devn)
-    if world == 1:
-        D_d = [torch.empty((M, N_LOCAL), dtype=torch.float16, device=devn) for _ in range(n_sets)]
-        G_d = None
-    else:
-        D_d = [torch.empty((M, N_LOCAL), dtype=torch.float16, device=devn) for _ in range(2)]
-        G_d = [torch.empty((world, M, N_LOCAL), dtype=torch.float16, device=devn) for _ in range(2)]
+    D_d = [torch.empty((M, N_LOCAL), dtype=torch.float16, device=devn) for _ in range(n_sets)]
+    layer = None
+    if world > 1:
+        from bare_metal_b200 import nsplit
+        # every rank owns the 4096-column slab [rank*4096, +4096) of the global weight matrix; the
+        # GEMM epilogue stores the slab into every rank's row-major output over NVLink (fused gather)
+        layer = nsplit.ColumnShardedLinear(W_d[0], sw_d, n_total, rank * N_LOCAL, mode=args.gather)
+        G_blocks = torch.empty((world, M, N_LOCAL), dtype=torch.float16, device=devn)
 
     def step(i: int):
         s = i % n_sets
         if world == 1:
             ig.w8a8_linear(A_d[s], W_d[s], D_d[s], sa_d, sw_d, M, N_LOCAL, K)
+        elif args.gather == "fused":
+            layer.W = W_d[s]
+            layer.forward_fused(A_d[s], sa_d)
         else:
-            ig.w8a8_linear(A_d[s], W_d[s], D_d[i % 2], sa_d, sw_d, M, N_LOCAL, K)
-            dist.all_gather_into_tensor(G_d[i % 2], D_d[i % 2])
+            layer.W = W_d[s]
+            layer.forward_nccl(A_d[s], sa_d, out=G_blocks, local=D_d[s])
 
     def sync():
         if world > 1:
@@ -225,7 +232,21 @@ def main() -> None:
     torch.cuda.synchronize()
     rows = np.array([0, 1, 127, 128, 2047, 4095])
     want = oracle.dequant_w8a8_f16(oracle.igemm_nt(np.ascontiguousarray(A_h[rows]), W_h), sa_h[rows], sw_h)
-    got = D_d[0].cpu().numpy()[rows]
+    if world == 1:
+        got = D_d[0].cpu().numpy()[rows]
+    elif args.gather == "fused":
+        full = layer._symmetric(M, devn)[0]
+        got = full[:, rank * N_LOCAL:(rank + 1) * N_LOCAL].cpu().numpy()[rows]
+        # the slab a PEER wrote into this rank's output must match that peer's weights too
+        peer = (rank + 1) % world
+        Wp = oracle.gen_int8((N_LOCAL, K), 0, sid("C2", f"W{peer}"))
+        swp = oracle.gen_scales(N_LOCAL, 0, sid("C2", f"sw{peer}"))
+        want_p = oracle.dequant_w8a8_f16(oracle.igemm_nt(np.ascontiguousarray(A_h[rows]), Wp), sa_h[rows], swp)
+        got_p = full[:, peer * N_LOCAL:(peer + 1) * N_LOCAL].cpu().numpy()[rows]
+        if not np.array_equal(got_p.view(np.uint16), want_p.view(np.uint16)):
+            raise SystemExit("parity check failed: the slab stored by a peer GPU disagrees with the CPU oracle")
+    else:
+        got = G_blocks[rank].cpu().numpy()[rows]
     if not np.array_equal(got.view(np.uint16), want.view(np.uint16)):
         raise SystemExit("parity check failed: the benchmarked kernel disagrees with the CPU oracle")
 
@@ -277,7 +298,7 @@ def main() -> None:
     ke0.record()
     for i in range(args.steps):
         s = i % n_sets
-        ig.w8a8_linear(A_d[s], W_d[s], D_d[s % len(D_d)], sa_d, sw_d, M, N_LOCAL, K)
+        ig.w8a8_linear(A_d[s], W_d[s], D_d[s], sa_d, sw_d, M, N_LOCAL, K)
     ke1.record()
     torch.cuda.synchronize()
     kern_ms = ke0.elapsed_time(ke1) / args.steps
@@ -288,9 +309,20 @@ def main() -> None:
                 "peak_note": f"2 x cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s, of {peaks['source']}); "
                              f"INT8 runs at twice the bf16 rate on this tensor core",
                 "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
-                "kernel": "igemm_dense_kernel<256,false,EPI_F16_ROWCOL>", "kernel_ms": kern_ms,
+                "kernel": "igemm_dense_pair_kernel<false,EPI_F16_ROWCOL>", "kernel_ms": kern_ms,
                 "algorithmic_bytes": set_bytes,
                 "traffic": TRAFFIC_BYTES_NCU}
+
+    if world > 1:
+        # fused GEMM + gather: the slower of the tensor time and the bytes a rank must RECEIVE over NVLink
+        link_gbs = 770.0                                        # measured peer-copy bandwidth per direction
+        recv_bytes = 2.0 * M * N_LOCAL * (world - 1)
+        t_link_ms = recv_bytes / (link_gbs * 1e9) * 1e3
+        target_ms = max(kern_ms, t_link_ms)
+        roofline["fused_collective"] = {"bound": "nvlink" if t_link_ms > kern_ms else "tensor",
+                                        "recv_bytes_per_rank": recv_bytes, "link_gb_per_s": link_gbs,
+                                        "target_ms": target_ms, "achieved_ms": ms_step,
+                                        "frac": target_ms / ms_step, "gemm_only_ms": kern_ms}
 
     # ---- end to end through the C ABI with host buffers --------------------------------------------
     e2e = None
@@ -341,9 +373,11 @@ def main() -> None:
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "s8*s8->s32 (fp32 scale, fp16 out)", "data": "synthetic",
                 "config": {"workload": f"C2 W8A8 GEMM M={M} K={K} N={n_total} ({N_LOCAL} weight columns per GPU)",
-                           "parallelism": f"n-split x{world}" + ("" if world == 1 else " + NCCL all-gather of the fp16 output"),
+                           "parallelism": f"n-split x{world}" + ("" if world == 1 else (
+                               " + all-gather of the fp16 output fused into the GEMM epilogue (peer TMA stores)"
+                               if args.gather == "fused" else " + NCCL all-gather of the fp16 output")),
                            "l2": f"{n_sets} rotating operand sets ({n_sets * set_bytes / 2**20:.0f} MiB) exceed the 126 MiB L2",
-                           "tile": "128x256x128, 4-stage TMA ring, 2 TMEM accumulators"},
+                           "tile": "CTA pairs (cta_group::2), 256x256x128 per pair, 5-stage TMA ring, 2 TMEM accumulators"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps,
                 "clocks": clocks, "extras": extras}
         print(json.dumps(line), flush=True)

@@ -74,6 +74,17 @@ int bm_igemm_i8_f32_perchannel(const int8_t *A, const int8_t *B, float *C, int M
 int bm_w8a8_f16(const int8_t *X, const int8_t *W, uint16_t *D, const float *sa_m, const float *sw_n,
                 int M, int N, int K, int64_t ldd, int w_layout, void *stream);
 
+/* N-split W8A8 linear fused with the all-gather of its output (no reference counterpart; the
+ * reference is single-GPU).  The rank computes its column slab D[:, slab] exactly as bm_w8a8_f16
+ * and the epilogue stores every finished box to the `n_peers` (<= 8) destinations in `D_peers`:
+ * HOST array of DEVICE pointers, each already pointing at the slab's first column inside that
+ * GPU's [M x N_total] output (peer-mapped memory for the other GPUs, e.g. symmetric memory).
+ * `ldd` = N_total.  Plain TMA stores, no multicast.  The caller orders the kernel against its peers
+ * (a barrier across the group after the launch) before anyone reads D. */
+int bm_w8a8_f16_gather(const int8_t *X, const int8_t *W, uint16_t *const *D_peers, int n_peers,
+                       const float *sa_m, const float *sw_n, int M, int N, int K, int64_t ldd,
+                       int w_layout, void *stream);
+
 /* One-time weight repack B[K x N] -> W[N x K] (excluded from GEMM timing). */
 int bm_pack_b_kn_to_nk(const int8_t *B_kn, int8_t *W_nk, int K, int N, void *stream);
 
