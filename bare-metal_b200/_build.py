@@ -15,6 +15,31 @@ NVCC_FLAGS = [
 ]
 
 
+HOST_DIR = os.path.join(PKG_DIR, "host")
+HOST_BIN = os.path.join(HOST_DIR, "bin")
+HOST_PROGRAMS = ("bench_igemm", "bench_sparse")
+
+
+def build_host(force: bool = False) -> list[str]:
+    """Compile the C++ bench drivers (host code only) against libbm_igemm.so; returns their paths."""
+    build(force=False)
+    nvcc = os.environ.get("NVCC", "nvcc")
+    os.makedirs(HOST_BIN, exist_ok=True)
+    include = os.path.join(os.path.dirname(PKG_DIR), "include")
+    out = []
+    for name in HOST_PROGRAMS:
+        src, exe = os.path.join(HOST_DIR, name + ".cpp"), os.path.join(HOST_BIN, name)
+        deps = [src, os.path.join(HOST_DIR, "host_common.h"), LIB_PATH]
+        if force or not os.path.exists(exe) or any(os.path.getmtime(d) > os.path.getmtime(exe) for d in deps):
+            cmd = [nvcc, "-O2", "-std=c++17", "-I" + include, "-I" + HOST_DIR, "-o", exe, src, "-L" + LIB_DIR,
+                   "-lbm_igemm", "-Xlinker", "-rpath," + "$ORIGIN/../../lib", "--cudart", "static"]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError("nvcc failed on " + name + ":\n" + res.stdout + res.stderr)
+        out.append(exe)
+    return out
+
+
 def _sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh")))
 

@@ -1,0 +1,123 @@
+// bench_sparse.cpp — C++ driver for the 2:4 sparse INT8 GEMM, the counterpart of the reference's
+// kernels/gemm/igemm/bench_sparse.cu with its cubin load replaced by a call into libbm_igemm.so.
+//
+//   ./bench_sparse [M] [N] [K]         (default 256 256 256; M, N % 16 == 0, K % 32 == 0)
+//
+// Same flow and stdout contract (bench_sparse.cu:19-103): libc-rand() 2:4 generator with seed 42,
+// compressor to values + uint32 metadata words, B from srand(137) without zeros, exact int32 CPU
+// reference scaled by (1/127)^2, 0.5/0.1 AND-logic check, and for M >= 512 a timed run (5 warm-up,
+// 50 launches) printed as "<ms> ms  <eff> eff GFLOPS  <dense> dense-equiv GFLOPS".
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "host_common.h"
+
+// 2 of every 4 positions non-zero; rows r and r+8 of a 16-row tile share positions — sparse_meta_int8.h:65-105
+static void gen_sparse(int8_t* A, int M, int K, unsigned seed) {
+    srand(seed);
+    memset(A, 0, (size_t)M * K);
+    for (int mt = 0; mt < M / 16; ++mt)
+        for (int gid = 0; gid < 8; ++gid) {
+            const int lo = mt * 16 + gid, hi = lo + 8;
+            for (int g = 0; g < K / 4; ++g) {
+                int perm[4] = {0, 1, 2, 3};
+                for (int i = 3; i >= 2; --i) { int j = rand() % (i + 1); int t = perm[i]; perm[i] = perm[j]; perm[j] = t; }
+                int p0 = perm[2], p1 = perm[3];
+                if (p0 > p1) { int t = p0; p0 = p1; p1 = t; }
+                int8_t v[4];
+                for (int i = 0; i < 4; ++i) do { v[i] = (int8_t)((rand() % 255) - 127); } while (v[i] == 0);
+                A[(size_t)lo * K + g * 4 + p0] = v[0]; A[(size_t)lo * K + g * 4 + p1] = v[1];
+                A[(size_t)hi * K + g * 4 + p0] = v[2]; A[(size_t)hi * K + g * 4 + p1] = v[3];
+            }
+        }
+}
+// kept values + one metadata word per (16-row tile, 32-wide K step, gid) — sparse_meta_int8.h:116-178
+static void compress(const int8_t* A, int M, int K, int8_t* comp, uint32_t* meta) {
+    const int ks = K / 32;
+    memset(meta, 0, (size_t)(M / 16) * ks * 8 * 4);
+    for (int m = 0; m < M; ++m)
+        for (int s = 0; s < ks; ++s) {
+            uint32_t nib = 0;
+            for (int g = 0; g < 8; ++g) {
+                const int8_t* v = &A[(size_t)m * K + s * 32 + g * 4];
+                int i0 = -1, i1 = -1;
+                for (int i = 0; i < 4; ++i)
+                    if (v[i] != 0) { if (i0 < 0) i0 = i; else if (i1 < 0) { i1 = i; break; } }
+                if (i0 < 0) i0 = 0;
+                if (i1 < 0) i1 = 1;
+                comp[(size_t)m * (K / 2) + s * 16 + g * 2] = v[i0];
+                comp[(size_t)m * (K / 2) + s * 16 + g * 2 + 1] = v[i1];
+                nib |= (((uint32_t)i1 << 2) | (uint32_t)i0) << (g * 4);
+            }
+            if (m % 16 < 8) meta[((size_t)(m / 16) * ks + s) * 8 + (m % 16) % 8] = nib;
+        }
+}
+
+int main(int argc, char** argv) {
+    int M = argc > 1 ? atoi(argv[1]) : 256, N = argc > 2 ? atoi(argv[2]) : M, K = argc > 3 ? atoi(argv[3]) : M;
+    if (M % 16 != 0 || N % 16 != 0 || K % 32 != 0) {
+        fprintf(stderr, "M, N must be multiples of 16; K must be multiple of 32\n");
+        return 1;
+    }
+    printf("=== Sparse INT8 GEMM Benchmark (libbm_igemm, sm_100a tcgen05.mma.sp) ===\n");
+    printf("M=%d  N=%d  K=%d\n\n", M, N, K);
+    cudaDeviceProp prop;
+    CHECK_CUDA(cudaGetDeviceProperties(&prop, 0));
+    printf("Device: %s\n\n", prop.name);
+
+    const size_t na = (size_t)M * K, nb = (size_t)K * N, nc = (size_t)M * N, nmeta = (size_t)(M / 16) * (K / 32) * 8;
+    std::vector<int8_t> A(na), comp(na / 2), B(nb);
+    std::vector<uint32_t> meta(nmeta);
+    std::vector<int32_t> ref_i(nc, 0);
+    std::vector<float> ref(nc), out(nc);
+    const float sa = 1.0f / 127.0f, sb = 1.0f / 127.0f;
+    gen_sparse(A.data(), M, K, 42);
+    compress(A.data(), M, K, comp.data(), meta.data());
+    srand(137);
+    for (size_t i = 0; i < nb; ++i) { int8_t v; do { v = (int8_t)((rand() % 255) - 127); } while (v == 0); B[i] = v; }
+    for (int r = 0; r < M; ++r)                                   // sparse_meta_int8.h:190-208
+        for (int k = 0; k < K; ++k) {
+            const int8_t a = A[(size_t)r * K + k];
+            if (a == 0) continue;
+            const int8_t* b = &B[(size_t)k * N];
+            int32_t* c = &ref_i[(size_t)r * N];
+            for (int n = 0; n < N; ++n) c[n] += (int32_t)a * (int32_t)b[n];
+        }
+    const float dq = sa * sb;
+    for (size_t i = 0; i < nc; ++i) ref[i] = (float)ref_i[i] * dq;
+
+    int8_t *dComp, *dB;
+    float* dC;
+    uint32_t* dMeta;
+    CHECK_CUDA(cudaMalloc(&dComp, na / 2)); CHECK_CUDA(cudaMalloc(&dB, nb)); CHECK_CUDA(cudaMalloc(&dC, nc * 4));
+    CHECK_CUDA(cudaMalloc(&dMeta, nmeta * 4));
+    CHECK_CUDA(cudaMemcpy(dComp, comp.data(), na / 2, cudaMemcpyHostToDevice));
+    CHECK_CUDA(cudaMemcpy(dB, B.data(), nb, cudaMemcpyHostToDevice));
+    CHECK_CUDA(cudaMemcpy(dMeta, meta.data(), nmeta * 4, cudaMemcpyHostToDevice));
+    auto launch = [&]() { CHECK_BM(bm_igemm_sparse_f32(dComp, dB, dC, dMeta, M, N, K, sa, sb, nullptr)); };
+
+    CHECK_CUDA(cudaMemset(dC, 0, nc * 4));
+    launch();
+    CHECK_CUDA(cudaDeviceSynchronize());
+    CHECK_CUDA(cudaMemcpy(out.data(), dC, nc * 4, cudaMemcpyDeviceToHost));
+    const CheckOutcome r = check_and_logic(out.data(), ref.data(), (int)nc, 0.5f, 0.1f);
+    print_check("igemm_sparse_tiled (INT8)", r);
+
+    if (M >= 512) {
+        for (int i = 0; i < 5; ++i) launch();
+        CHECK_CUDA(cudaDeviceSynchronize());
+        EventTimer t;
+        t.start();
+        for (int i = 0; i < 50; ++i) launch();
+        const float ms = t.stop_ms() / 50.f;
+        const double eff = 2.0 * M * N * (K / 2.0) / (ms / 1000.0) / 1e9, dense = 2.0 * M * N * (double)K / (ms / 1000.0) / 1e9;
+        printf("  %-34s %9.3f ms  %8.0f eff GFLOPS  %8.0f dense-equiv GFLOPS\n", "igemm_sparse_tiled", ms, eff, dense);
+    }
+    int code = 0;
+    CHECK_BM(bm_last_device_status(&code));
+    if (code != 0) { fprintf(stderr, "device status %d\n", code); return EXIT_FAILURE; }
+    cudaFree(dComp); cudaFree(dB); cudaFree(dC); cudaFree(dMeta);
+    bm_shutdown();
+    return r.errors ? EXIT_FAILURE : EXIT_SUCCESS;
+}
