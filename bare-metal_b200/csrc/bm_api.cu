@@ -183,6 +183,27 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
         const int pair_tiles = p.tiles_m * p.tiles_n;
         const int max_pairs = dev->sm_count / 2;
         const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+        // Tail split (BM_TAIL_SPLIT=S, S in 2..4): cut each tile of a partly filled last wave into S
+        // K ranges for different pairs.  Off by default: at 4096^3 (34 tail tiles on 74 pairs, S = 2)
+        // it was measured 15 % SLOWER (69.5 vs 60.3 us on the same box) — parking 128 KiB per CTA,
+        // the fence/atomic hand-off and re-reading both parts cost more than the half tile they save.
+        {
+            const int rem = pair_tiles % pairs;
+            int split = 1;
+            if (const char* e = getenv("BM_TAIL_SPLIT")) {
+                const int f = atoi(e);
+                if (f > 1 && f <= 4 && rem > 0 && pair_tiles > pairs && f * rem <= pairs && f <= p.k_blocks) split = f;
+            }
+            if (split > 1) {
+                const size_t slice_ints = static_cast<size_t>(kPairNC) * 32;
+                const size_t ws_bytes = static_cast<size_t>(rem) * split * 2 * kEpiWarps * slice_ints * sizeof(int32_t);
+                if (int rc = ensure_split_k(dev, ws_bytes, static_cast<size_t>(rem) * 2 * kEpiWarps)) return rc;
+                p.tail_first = pair_tiles - rem;
+                p.tail_split = split;
+                p.sk_workspace = static_cast<int32_t*>(dev->sk_workspace);
+                p.sk_counters = dev->sk_counters;
+            }
+        }
 #define BM_PAIR_CASE(E)                                                                         \
     case E:                                                                                     \
         return b_mn ? launch_dense_pair<true, E>(map_a, map_b, map_out, p, pairs, stream)       \

@@ -246,10 +246,33 @@ struct OutMaps {
     CUtensorMap m[kMaxOutMaps];
 };
 
-template <int EPI, int NC>
-__device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const OutMaps& maps, int n_maps,
-                                                      uint32_t taddr, int row0, int lane, int col0,
-                                                      const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem) {
+// Where the 32-column chunks of a drain come from: tensor memory (asynchronous loads, waited for
+// just before use) or the parked partial sums of a split tile (added up on the fly).
+struct TmemSource {
+    uint32_t taddr;
+    __device__ __forceinline__ void issue(int c, uint32_t (&r)[32]) const { tmem_ld_32x32(taddr + c * 32, r); }
+    __device__ __forceinline__ void wait() const { tmem_ld_wait(); }
+};
+template <class PartPtr>
+struct ParkedSource {
+    PartPtr part_ptr;      // part index -> this warp's slice of that part
+    int parts, lane;
+    __device__ __forceinline__ void issue(int c, uint32_t (&r)[32]) const {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) r[k] = 0;
+        for (int part = 0; part < parts; ++part) {
+            const int32_t* s = part_ptr(part) + c * 32 * 32 + lane;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) r[k] += static_cast<uint32_t>(__ldcg(s + k * 32));
+        }
+    }
+    __device__ __forceinline__ void wait() const {}
+};
+
+template <int EPI, int NC, class Source>
+__device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const OutMaps& maps, int n_maps, const Source& src,
+                                               int row0, int lane, int col0, const EpiStrip<NC>* strip, float lane_s,
+                                               uint32_t stage_smem) {
     using T = typename OutType<EPI>::type;
     static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
     constexpr int CHUNKS = NC / 32;
@@ -261,14 +284,14 @@ __device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, c
     const int sw = lane & 7;                                 // 128-byte swizzle: piece index ^ (row % 8)
 
     uint32_t rr[2][32];
-    if (col0 < p.cols) tmem_ld_32x32(taddr, rr[0]);
+    if (col0 < p.cols) src.issue(0, rr[0]);
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
         const int cur = c & 1;
         const bool live = col0 + c * 32 < p.cols;            // warp-uniform
         if (live) {
-            tmem_ld_wait();
-            if (c + 1 < CHUNKS && col0 + (c + 1) * 32 < p.cols) tmem_ld_32x32(taddr + (c + 1) * 32, rr[cur ^ 1]);
+            src.wait();
+            if (c + 1 < CHUNKS && col0 + (c + 1) * 32 < p.cols) src.issue(c + 1, rr[cur ^ 1]);
             if (c % CHUNKS_PER_BOX == 0) {
                 // the strip may still be read by the previous box's store
                 if (lane == 0) bulk_wait_read_all();
@@ -302,6 +325,13 @@ __device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, c
             }
         }
     }
+}
+
+template <int EPI, int NC>
+__device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const OutMaps& maps, int n_maps,
+                                                      uint32_t taddr, int row0, int lane, int col0,
+                                                      const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem) {
+    drain_tma_from<EPI, NC>(p, maps, n_maps, TmemSource{taddr}, row0, lane, col0, strip, lane_s, stage_smem);
 }
 
 }  // namespace bm

@@ -55,6 +55,13 @@ struct DenseParams {
     int tiles_m, tiles_n, k_blocks;
     int* status;
     int n_out;                 // number of output destinations in the OutMaps argument (1 unless gathering)
+    // tail split (CTA-pair kernel): tiles [0, tail_first) run whole, wave after wave; each of the
+    // remaining tiles is cut into `tail_split` K ranges handled by different pairs, so the last,
+    // partly filled wave takes 1/tail_split of a tile time.  Partial sums meet in sk_workspace and
+    // the part that arrives last (per epilogue warp, counted in sk_counters) finishes the tile.
+    int tail_first, tail_split;
+    int* sk_counters;          // [tail tiles][2 CTAs][epilogue warps], zero between launches
+    int32_t* sk_workspace;     // [tail tiles][tail_split][2 CTAs][epilogue warps][NC x 32]
     unsigned long long* dbg_buf;   // bring-up only: per-CTA stall cycle counters (8 per CTA) when non-null
 };
 

@@ -37,6 +37,41 @@ constexpr int kPairNC = kPairBN / 2;                // columns drained per epilo
 constexpr int kPairStripOffset = kPairBarOffset + (2 * kPairStages + 5) * 8 + 16;
 constexpr int kPairSmemBytes = kPairStripOffset + kEpiWarps * (int)sizeof(EpiStrip<kPairNC>) + 1024;
 
+// Work of one CTA pair: whole tiles pair, pair+P, ... below `tail_first`, then (if the tail is
+// split) one K range of one tail tile.
+struct PairWork {
+    int tile, kb0, kb1, part;           // part < 0: the whole tile
+};
+struct PairWorkIter {
+    int next_tile, pairs, tiles, tail_first, split, k_blocks, pair;
+    bool tail_done;
+    __device__ PairWorkIter(int pair_, int pairs_, int tiles_, int k_blocks_, int tail_first_, int split_)
+        : next_tile(pair_), pairs(pairs_), tiles(tiles_), tail_first(split_ > 1 ? tail_first_ : tiles_), split(split_),
+          k_blocks(k_blocks_), pair(pair_), tail_done(false) {}
+    __device__ bool next(PairWork& w) {
+        if (next_tile < tail_first) {
+            w.tile = next_tile;
+            w.kb0 = 0;
+            w.kb1 = k_blocks;
+            w.part = -1;
+            next_tile += pairs;
+            return true;
+        }
+        if (split > 1 && !tail_done) {
+            tail_done = true;
+            const int unit = pair;                                   // pair u takes part u % split of tail tile u / split
+            if (unit < (tiles - tail_first) * split) {
+                w.tile = tail_first + unit / split;
+                w.part = unit % split;
+                w.kb0 = static_cast<int>(static_cast<long long>(k_blocks) * w.part / split);
+                w.kb1 = static_cast<int>(static_cast<long long>(k_blocks) * (w.part + 1) / split);
+                return true;
+            }
+        }
+        return false;
+    }
+};
+
 template <bool B_MN, int EPI>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -98,10 +133,13 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             long long t_wait = 0, t_begin = clock64();
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
+            PairWork w;
+            while (ok && work.next(w)) {
+                const int tile = w.tile;
                 const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
                 const int n0 = (tile / p.tiles_m) * kPairBN + static_cast<int>(rank) * kPairHalfN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     const long long tw = clock64();
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
@@ -125,14 +163,16 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             long long t_full = 0, t_acc = 0, t_begin = clock64();
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
+            PairWork w;
+            while (ok && work.next(w)) {
                 const long long ta = clock64();
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
                 t_acc += clock64() - ta;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kPairBN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     const long long tf = clock64();
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
@@ -148,7 +188,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const uint64_t b_desc =
                             B_MN ? make_smem_desc(b_addr + ks * (kUmmaK * 128), 128 * kBK, 1024, SWIZZLE_128B_DESC)
                                  : make_smem_desc(b_addr + ks * kUmmaK, 0, 1024, SWIZZLE_128B_DESC);
-                        mma_i8_pair(d_tmem, a_desc, b_desc, idesc, (kb | ks) != 0 ? 1u : 0u);
+                        mma_i8_pair(d_tmem, a_desc, b_desc, idesc, (kb != w.kb0 || ks != 0) ? 1u : 0u);
                     }
                     tc_commit_pair(empty_bar(stage));                       // this CTA's producer
                     tc_commit_pair(mapa_shared(empty_bar(stage), 1));       // the peer's producer
@@ -177,7 +217,10 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         EpiStrip<kPairNC>* strip = reinterpret_cast<EpiStrip<kPairNC>*>(smem_gen + kPairStripOffset) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
         long long t_epi_wait = 0, t_epi_begin = clock64();
-        for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+        PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
+        PairWork w;
+        while (work.next(w)) {
+            const int tile = w.tile;
             const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
             const int n0 = (tile / p.tiles_m) * kPairBN + half * kPairNC;
             const int row = m0 + quarter * 32 + lane;
@@ -190,14 +233,48 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             tc_fence_after_sync();
             const uint32_t taddr =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN + half * kPairNC;
-            if (p.epi.tma_ok)
-                drain_accumulator_tma<EPI, kPairNC>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip, lane_s,
-                                                    smem_base + kPairStoreOffset + (warp - 2) * kStoreBoxBytes);
-            else
-                drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, p.epi.cols, strip, lane_s);
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
+            const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kStoreBoxBytes;
+            if (w.part < 0) {
+                if (p.epi.tma_ok)
+                    drain_accumulator_tma<EPI, kPairNC>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
+                                                        lane_s, my_stage);
+                else
+                    drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, p.epi.cols, strip, lane_s);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
+            } else {
+                // one K range of a split tail tile: park the raw sums; whoever completes the slice finishes it
+                constexpr int SLICE = kPairNC * 32;
+                const int tail_idx = tile - p.tail_first;
+                const int slice_id = static_cast<int>(rank) * kEpiWarps + (warp - 2);
+                auto part_of = [&](int part) -> int32_t* {
+                    return p.sk_workspace +
+                           ((static_cast<size_t>(tail_idx) * p.tail_split + part) * 2 * kEpiWarps + slice_id) * SLICE;
+                };
+                park_accumulator<kPairNC>(taddr, part_of(w.part), lane);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
+                __threadfence();
+                int last = 0;
+                int* counter = p.sk_counters + tail_idx * 2 * kEpiWarps + slice_id;
+                if (lane == 0) {
+                    last = (atomicAdd(counter, 1) == p.tail_split - 1);
+                    if (last) *counter = 0;
+                }
+                last = __shfl_sync(0xFFFFFFFFu, last, 0);
+                if (last) {
+                    __threadfence();
+                    auto ptr = [&](int part) -> const int32_t* { return part_of(part); };
+                    if (p.epi.tma_ok)
+                        drain_tma_from<EPI, kPairNC>(p.epi, maps_out, p.n_out,
+                                                     ParkedSource<decltype(ptr)>{ptr, p.tail_split, lane},
+                                                     m0 + quarter * 32, lane, n0, strip, lane_s, my_stage);
+                    else
+                        finish_parked<EPI, kPairNC, false>(p.epi, ptr, p.tail_split, row, n0, p.epi.cols, strip, lane_s, lane);
+                }
+            }
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
         }

@@ -168,3 +168,37 @@ def test_bad_arguments_raise_on_the_gpu_too():
         ig.igemm_i32(a, a, c, 128, 128, 40, ig.BM_B_NK)
     with pytest.raises(ig.BmError):
         ig.igemm_i32(a, a, c.float(), 128, 128, 32, ig.BM_B_NK)     # wrong output dtype
+
+
+@pytest.mark.parametrize("M,N,K,layout", [(2560, 2304, 512, ig.BM_B_NK), (2500, 2320, 272, ig.BM_B_KN),
+                                          (2816, 2048, 1024, ig.BM_B_NK)])
+def test_tail_split_of_the_last_wave(M, N, K, layout):
+    """More 256x256 tiles than CTA pairs with a partly filled last wave: its tiles are cut into K
+    ranges for different pairs and the partial sums are added exactly (int32), then dequantised once.
+    Run twice so the self-resetting arrival counters are exercised."""
+    A = oracle.gen_int8((M, K), 11, 1)
+    B = oracle.gen_int8((K, N), 11, 2)
+    acc = oracle.igemm(A, B, threads=0)
+    sa, sw = oracle.gen_scales(M, 11, 3), oracle.gen_scales(N, 11, 4)
+    want16 = oracle.dequant_w8a8_f16(acc, sa, sw).view(np.uint16)
+    Bd = T(B) if layout == ig.BM_B_KN else T(B.T)
+    from _gpu import env
+    with env(BM_TAIL_SPLIT=2):
+        for _ in range(2):
+            C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
+            ig.igemm_i32(T(A), Bd, C, M, N, K, layout)
+            assert_clean_status()
+            assert np.array_equal(C.cpu().numpy(), acc)
+            D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+            ig.w8a8_linear(T(A), Bd, D, T(sa), T(sw), M, N, K, layout)
+            assert_clean_status()
+            assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
+        # through the unaligned (direct-store) path
+        wide = torch.zeros((M, N + 1), dtype=torch.int32, device=dev())
+        ig.igemm_i32(T(A), Bd, wide[:, :N], M, N, K, layout)
+        assert_clean_status()
+        assert np.array_equal(wide.cpu().numpy()[:, :N], acc)
+    # same integers with the split off (the default)
+    C2 = torch.empty((M, N), dtype=torch.int32, device=dev())
+    ig.igemm_i32(T(A), Bd, C2, M, N, K, layout)
+    assert np.array_equal(C2.cpu().numpy(), acc)
