@@ -47,8 +47,7 @@ static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured[dev] = true;
     }
-    kern<<<grid, kDenseThreads, Cfg::SMEM_BYTES, stream>>>(ma, mb, mo, p);
-    BM_CUDA_TRY(cudaGetLastError());
+    BM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(kDenseThreads), Cfg::SMEM_BYTES, stream, 1, ma, mb, mo, p));
     return BM_OK;
 }
 
@@ -64,19 +63,7 @@ static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
         configured[dev] = true;
     }
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(2 * pairs);
-    cfg.blockDim = dim3(kDenseThreads);
-    cfg.dynamicSmemBytes = kPairSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    BM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, mo, p));
+    BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kPairSmemBytes, stream, 2, ma, mb, mo, p));
     return BM_OK;
 }
 
@@ -277,8 +264,7 @@ static int launch_sparse_inst(const CUtensorMap& ms, const CUtensorMap& md, cons
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured[dev] = true;
     }
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ms, md, p);
-    BM_CUDA_TRY(cudaGetLastError());
+    BM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, 1, ms, md, p));
     return BM_OK;
 }
 
@@ -294,19 +280,7 @@ static int launch_sparse_pair(const CUtensorMap& mw, const CUtensorMap& me, cons
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSpPairSmemBytes));
         configured[dev] = true;
     }
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(2 * pairs);
-    cfg.blockDim = dim3(kDenseThreads);
-    cfg.dynamicSmemBytes = kSpPairSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    BM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mw, me, mx, p));
+    BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kSpPairSmemBytes, stream, 2, mw, me, mx, p));
     return BM_OK;
 }
 
@@ -409,8 +383,22 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
     p.k_blocks = ceil_div(K, kSpKLogical);
     p.status = dev->status;
     const int num_tiles = p.tiles_r * p.tiles_c;
-    int grid = num_tiles < dev->sm_count ? num_tiles : dev->sm_count;
+    const int resident = dev->sm_count * (bn <= 64 ? 2 : 1);      // narrow tiles run two CTAs per SM
+    int grid = num_tiles < resident ? num_tiles : resident;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    // Row-balanced tiles for the decode shapes (packed weights, all tokens in one column tile): whole
+    // 128-row tiles would give some SMs two tiles and others one (224 tiles on 148 SMs); dealing the
+    // rows out in multiples of 8 keeps every SM streaming the same number of bytes.  BM_ROW_BALANCED=0
+    // switches it off.
+    p.sparse_rows = R;
+    if (mode == 1 && packed && p.tiles_c == 1 && num_tiles % resident != 0 && R >= 8 * resident) {
+        const char* e = getenv("BM_ROW_BALANCED");
+        if (!e || atoi(e) != 0) {
+            p.row_balanced = 1;
+            grid = resident;
+        }
+    }
 
     // Stream-K (BM_STREAM_K=1): the (tile, K block) units are dealt out evenly instead of whole tiles.
     // Off by default: on the decode shapes it was measured 1 % slower than whole tiles (33.5 vs
@@ -418,11 +406,11 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
     {
         const long long units = static_cast<long long>(num_tiles) * p.k_blocks;
         const char* force = getenv("BM_STREAM_K");
-        const bool want = force && atoi(force) != 0 && units >= 2;
+        const bool want = force && atoi(force) != 0 && units >= 2 && !p.row_balanced;
         if (want) {
-            grid = units < dev->sm_count ? static_cast<int>(units) : dev->sm_count;
-            const int epi_warps = bn >= 64 ? 8 : 4;
-            const size_t slice_ints = static_cast<size_t>(bn >= 64 ? bn / 2 : 32) * 32;
+            grid = units < resident ? static_cast<int>(units) : resident;
+            const int epi_warps = bn >= 128 ? 8 : 4;
+            const size_t slice_ints = static_cast<size_t>(bn >= 128 ? bn / 2 : (bn == 64 ? 64 : 32)) * 32;
             const size_t ws_bytes = static_cast<size_t>(grid) * 2 * epi_warps * slice_ints * sizeof(int32_t);
             if (int rc = ensure_split_k(dev, ws_bytes, static_cast<size_t>(num_tiles) * epi_warps)) return rc;
             p.stream_k = 1;

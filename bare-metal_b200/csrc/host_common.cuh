@@ -5,6 +5,7 @@
 #pragma once
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -175,6 +176,37 @@ inline int make_tensor_map_out(CUtensorMap* map, const void* base, uint64_t cols
         return BM_ERR_CUDA;
     }
     return BM_OK;
+}
+
+// Launch with programmatic stream serialization (and optionally a 2-CTA cluster): the kernel may be
+// scheduled while the previous kernel of the stream drains; it synchronises itself with
+// griddepcontrol.wait.  BM_NO_PDL=1 falls back to plain stream order (testing hook).
+template <class Kernel, class... Args>
+inline cudaError_t launch_pdl(Kernel kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
+                              Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    static const bool no_pdl = getenv("BM_NO_PDL") != nullptr;
+    if (!no_pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -114,6 +114,8 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    pdl_launch_dependents();      // the next kernel of the stream may start its own set-up
+    pdl_wait_prior_grid();        // nothing global is touched before the previous grid is complete
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer

@@ -124,6 +124,8 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     cluster_wait();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    pdl_launch_dependents();      // the next kernel of the stream may start its own set-up
+    pdl_wait_prior_grid();        // nothing global is touched before the previous grid is complete
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)

@@ -32,14 +32,19 @@ namespace bm {
 
 constexpr int kSpKLogical = 256;                 // logical K per stage
 constexpr int kSpMetaBytes = 4096;               // metadata bytes per (128-row block, k-block)
-constexpr int kSpSmemBudget = 216 * 1024;
+constexpr int kSpSmemBudget = 216 * 1024;         // one CTA per SM
+constexpr int kSpSmemBudgetNarrow = 100 * 1024;   // narrow token tiles (decode): two CTAs per SM
 
 template <int BN>
 struct SparseCfg {
     static constexpr int A_BYTES = kBM * 128;                     // 16 KiB compressed
     static constexpr int B_BYTES = BN * kSpKLogical;              // dense operand
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + kSpMetaBytes;
-    static constexpr int STAGES_RAW = kSpSmemBudget / STAGE_BYTES;
+    // Decode-shaped tiles (BN <= 64) take half an SM each: two CTAs per SM keep twice as many
+    // independent streams in flight and let the CTAs of the next launch settle in while the last
+    // ones of this launch drain.
+    static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
+    static constexpr int STAGES_RAW = (BN <= 32 ? kSpSmemBudgetNarrow : BN == 64 ? 108 * 1024 : kSpSmemBudget) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int E_COLS = STAGES * 8;                     // 2 x tcgen05.cp of 4 columns per stage
     static constexpr int ACC_BUFS = (2 * BN + E_COLS <= 512) ? 2 : 1;
@@ -48,8 +53,8 @@ struct SparseCfg {
     static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
                                    : COLS_NEEDED <= 256 ? 256 : 512;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int EPI_WARPS = BN >= 64 ? 8 : 4;            // two per lane quarter for wide tiles
-    static constexpr int NC = BN >= 64 ? BN / 2 : 32;             // accumulator columns drained per warp
+    static constexpr int EPI_WARPS = BN >= 128 ? 8 : 4;           // two per lane quarter for wide tiles
+    static constexpr int NC = BN >= 128 ? BN / 2 : (BN == 64 ? 64 : 32);   // accumulator columns drained per warp
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int STRIP_OFFSET = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16;
     static constexpr int SMEM_BYTES = STRIP_OFFSET + EPI_WARPS * (int)sizeof(EpiStrip<NC>) + 1024;
@@ -68,34 +73,57 @@ struct SparseParams {
     // may be shared by several CTAs; partial sums meet in `sk_workspace`, the part that arrives last
     // (per epilogue warp, counted in `sk_counters`) adds them up and runs the epilogue.  No CTA waits.
     int stream_k;
+    // row-balanced mode (packed weights, one column tile — the decode shapes): the rows of the
+    // sparse operand are dealt out evenly in multiples of 8, so a CTA's last tile may hold fewer
+    // than 128 rows and only those rows are fetched (the packed blocks are row-contiguous).
+    int row_balanced;
+    int sparse_rows;                   // rows of the sparse operand (R)
     int* sk_counters;                  // [tiles][epilogue warps], zero between launches (self-resetting)
     int32_t* sk_workspace;             // [CTAs][2: head / tail share][epilogue warps][NC x 32]
 };
 
-// One contiguous piece of work: k-blocks [kb0, kb1) of one tile.
+// One contiguous piece of work: k-blocks [kb0, kb1) of one tile; the tile covers rows
+// [row0, row0 + nrows) of the sparse operand (nrows = 128 except in row-balanced mode).
 struct WorkSegment {
-    int tile, kb0, kb1;
+    int tile, kb0, kb1, row0, nrows;
 };
 
 // Deals work to CTA `cta` of `ctas`.  Static mode: whole tiles cta, cta+ctas, ...  Stream-K mode: the
 // units [cta*U/ctas, (cta+1)*U/ctas) of the U = tiles*k_blocks (tile-major) units, cut at tile borders.
 struct WorkIter {
     long long u, u_end;
-    int tile, tiles, k_blocks, step;
-    bool stream_k;
-    __device__ WorkIter(bool sk, int cta, int ctas, int tiles_, int k_blocks_)
-        : tile(cta), tiles(tiles_), k_blocks(k_blocks_), step(ctas), stream_k(sk) {
-        const long long U = static_cast<long long>(tiles_) * k_blocks_;
+    int tile, tiles, k_blocks, step, tiles_r;
+    int row, row_end;                  // row-balanced mode
+    bool stream_k, row_balanced;
+    __device__ WorkIter(const SparseParams& p, int cta, int ctas, int tiles_)
+        : tile(cta), tiles(tiles_), k_blocks(p.k_blocks), step(ctas), tiles_r(p.tiles_r),
+          stream_k(p.stream_k != 0), row_balanced(p.row_balanced != 0) {
+        const long long U = static_cast<long long>(tiles_) * p.k_blocks;
         u = U * cta / ctas;
         u_end = U * (cta + 1) / ctas;
+        const long long r8 = (p.sparse_rows + 7) / 8;
+        row = static_cast<int>(r8 * cta / ctas) * 8;
+        row_end = static_cast<int>(r8 * (cta + 1) / ctas) * 8;
     }
     __device__ bool next(WorkSegment& s) {
+        if (row_balanced) {
+            if (row >= row_end) return false;
+            s.tile = 0;
+            s.kb0 = 0;
+            s.kb1 = k_blocks;
+            s.row0 = row;
+            s.nrows = row_end - row < 128 ? row_end - row : 128;
+            row += s.nrows;
+            return true;
+        }
+        s.nrows = 128;
         if (stream_k) {
             if (u >= u_end) return false;
             s.tile = static_cast<int>(u / k_blocks);
             s.kb0 = static_cast<int>(u % k_blocks);
             const long long left = u_end - u;
             s.kb1 = (s.kb0 + left < k_blocks) ? static_cast<int>(s.kb0 + left) : k_blocks;
+            s.row0 = (s.tile % tiles_r) * 128;
             u += s.kb1 - s.kb0;
             return true;
         }
@@ -103,6 +131,7 @@ struct WorkIter {
         s.tile = tile;
         s.kb0 = 0;
         s.kb1 = k_blocks;
+        s.row0 = (tile % tiles_r) * 128;
         tile += step;
         return true;
     }
@@ -114,7 +143,7 @@ __device__ __forceinline__ int stream_k_owner(long long u, long long U, int ctas
 }
 
 template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false>
-__global__ void __launch_bounds__(SparseCfg<BN>::THREADS, 1)
+__global__ void __launch_bounds__(SparseCfg<BN>::THREADS, SparseCfg<BN>::CTAS_PER_SM)
 igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_d,
                     const SparseParams p) {
     using Cfg = SparseCfg<BN>;
@@ -162,6 +191,8 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    pdl_launch_dependents();      // the next kernel of the stream may start its own set-up
+    pdl_wait_prior_grid();        // nothing global is touched before the previous grid is complete
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -170,11 +201,14 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             prefetch_tensormap(&map_d);
             uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
             bool ok = true;
-            WorkIter work(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, p.k_blocks);
+            WorkIter work(p, blockIdx.x, gridDim.x, num_tiles);
             WorkSegment seg;
             while (ok && work.next(seg)) {
-                const int rb = seg.tile % p.tiles_r;
-                const int r0 = rb * kBM;
+                const int r0 = seg.row0;
+                const int rb = r0 / kBM;                   // first 128-row block the tile touches
+                const int off0 = r0 % kBM;                 // rows of that block skipped (row-balanced mode only)
+                const int n0 = seg.nrows < kBM - off0 ? seg.nrows : kBM - off0;   // rows from block rb
+                const int n1 = seg.nrows - n0;                                    // rows from block rb + 1
                 const int c0 = (seg.tile / p.tiles_r) * BN;
                 const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) * p.k_blocks *
                                                              (PACKED ? kSpPackedBlock : kSpMetaBytes);
@@ -182,12 +216,25 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
                     const uint32_t bar = full_bar(stage);
-                    mbar_expect_tx(bar, Cfg::STAGE_BYTES);
-                    if constexpr (PACKED)      // pre-swizzled values: one linear 16 KiB copy
-                        bulk_load(a_smem0 + stage * Cfg::A_BYTES, meta_row + static_cast<size_t>(kb) * kSpPackedBlock,
-                                  Cfg::A_BYTES, bar);
-                    else
+                    if constexpr (PACKED) {
+                        // pre-swizzled, row-contiguous blocks: linear copies of exactly the rows of this tile
+                        // (row0 is a multiple of 8, so the swizzle phase of a row is the same in the tile)
+                        mbar_expect_tx(bar, static_cast<uint32_t>(seg.nrows) * (128 + 32) + Cfg::B_BYTES);
+                        const uint8_t* blk0 = meta_row + static_cast<size_t>(kb) * kSpPackedBlock;
+                        const uint8_t* blk1 = blk0 + static_cast<size_t>(p.k_blocks) * kSpPackedBlock;
+                        const uint32_t a_dst = a_smem0 + stage * Cfg::A_BYTES;
+                        const uint32_t e_dst = e_smem0 + stage * kSpMetaBytes;
+                        bulk_load(a_dst, blk0 + off0 * 128, n0 * 128, bar);
+                        if (n1 > 0) bulk_load(a_dst + n0 * 128, blk1, n1 * 128, bar);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            bulk_load(e_dst + j * 2048, blk0 + Cfg::A_BYTES + j * 2048 + off0 * 16, n0 * 16, bar);
+                            if (n1 > 0) bulk_load(e_dst + j * 2048 + n0 * 16, blk1 + Cfg::A_BYTES + j * 2048, n1 * 16, bar);
+                        }
+                    } else {
+                        mbar_expect_tx(bar, Cfg::STAGE_BYTES);
                         tma_load_2d(a_smem0 + stage * Cfg::A_BYTES, &map_s, bar, kb * 128, r0);
+                    }
                     const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
                     if constexpr (DENSE_MN) {
 #pragma unroll
@@ -199,10 +246,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                         for (int j = 0; j < 2; ++j)          // [BN rows x 128 K bytes] per box
                             tma_load_2d(b_addr + j * (BN * 128), &map_d, bar, kb * kSpKLogical + j * 128, c0);
                     }
-                    if constexpr (PACKED)
-                        bulk_load(e_smem0 + stage * kSpMetaBytes,
-                                  meta_row + static_cast<size_t>(kb) * kSpPackedBlock + Cfg::A_BYTES, kSpMetaBytes, bar);
-                    else
+                    if constexpr (!PACKED)
                         bulk_load(e_smem0 + stage * kSpMetaBytes, meta_row + static_cast<size_t>(kb) * kSpMetaBytes,
                                   kSpMetaBytes, bar);
                     issued |= 1u << stage;
@@ -225,7 +269,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             constexpr uint32_t idesc = make_idesc_i8(kBM, BN, DENSE_MN, true);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            WorkIter work(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, p.k_blocks);
+            WorkIter work(p, blockIdx.x, gridDim.x, num_tiles);
             WorkSegment seg;
             while (ok && work.next(seg)) {
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
@@ -278,12 +322,17 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
         const int half = (warp - 2) >> 2;                     // 0 unless the tile is drained by 8 warps
         EpiStrip<Cfg::NC>* strip = reinterpret_cast<EpiStrip<Cfg::NC>*>(smem_gen + Cfg::STRIP_OFFSET) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
-        WorkIter work(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, p.k_blocks);
+        WorkIter work(p, blockIdx.x, gridDim.x, num_tiles);
         WorkSegment seg;
         while (work.next(seg)) {
-            const int r0 = (seg.tile % p.tiles_r) * kBM;
+            const int r0 = seg.row0;
             const int c0 = (seg.tile / p.tiles_r) * BN + half * Cfg::NC;
             const int lane_coord = r0 + quarter * 32 + lane;      // row of the sparse operand
+            EpilogueParams epi = p.epi;                           // rows beyond this tile's share are not ours to write
+            if (seg.nrows < kBM) {
+                if (TRANSPOSED) epi.cols = epi.cols < r0 + seg.nrows ? epi.cols : r0 + seg.nrows;
+                else            epi.rows = epi.rows < r0 + seg.nrows ? epi.rows : r0 + seg.nrows;
+            }
             // never write past this tile's own columns when the tile is narrower than a 32-column chunk
             int c_limit = TRANSPOSED ? p.epi.rows : p.epi.cols;
             if (BN < 32 && c_limit > c0 + BN) c_limit = c0 + BN;
@@ -295,7 +344,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * Cfg::NC;
             if (whole) {
-                drain_accumulator<EPI, Cfg::NC, TRANSPOSED>(p.epi, taddr, lane_coord, c0, c_limit, strip, lane_s);
+                drain_accumulator<EPI, Cfg::NC, TRANSPOSED>(epi, taddr, lane_coord, c0, c_limit, strip, lane_s);
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty_bar(acc));
@@ -329,7 +378,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                 if (last) {
                     __threadfence();
                     finish_parked<EPI, Cfg::NC, TRANSPOSED>(
-                        p.epi, [&](int part) -> const int32_t* { return share_of(cta_first + part); }, parts,
+                        epi, [&](int part) -> const int32_t* { return share_of(cta_first + part); }, parts,
                         lane_coord, c0, c_limit, strip, lane_s, lane);
                 }
             }

@@ -99,6 +99,8 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     cluster_wait();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    pdl_launch_dependents();      // the next kernel of the stream may start its own set-up
+    pdl_wait_prior_grid();        // nothing global is touched before the previous grid is complete
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer (both CTAs)

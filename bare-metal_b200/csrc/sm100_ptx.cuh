@@ -56,6 +56,19 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ----------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every GEMM kernel lets the next kernel of the stream be
+// scheduled early (its CTAs take SMs as this grid's CTAs retire and run their set-up), and
+// itself waits here — before its first global read or write — until the grid before it has
+// completed and its memory is visible.  Without the launch attribute both are no-ops.
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait_prior_grid() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------------------
 // mbarrier
 // ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

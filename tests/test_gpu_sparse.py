@@ -231,3 +231,28 @@ def test_sparse_weights_on_cta_pairs(M, N, K):
         ig.w8a8_sparse_linear(T(X), T(comp), tiled, D, T(sa), T(sw), M, N, K)
     assert_clean_status()
     assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)) <= 1
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 2000, 512), (1, 28672, 256), (64, 1504, 1024), (5, 4097, 288)])
+def test_row_balanced_decode_tiles(M, N, K):
+    """Decode shapes on packed weights: rows are dealt to the SMs in multiples of 8 (ragged last
+    tiles fetch only their own rows); results must not depend on where the cuts fall."""
+    from _gpu import env
+    comp, nib = oracle.gen_sparse_rows(N, K, 5, 61)
+    X = oracle.gen_int8((M, K), 5, 62)
+    want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
+    packed = ig.sp_pack_weights(T(comp), T(nib), ig.BM_META_ROWS, N, K)
+    sa, sw = oracle.gen_scales(M, 5, 3), oracle.gen_scales(N, 5, 4)
+    want16 = oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)
+    for balanced in (1, 0):
+        with env(BM_ROW_BALANCED=balanced):
+            guard = torch.full((M + 2, N), 0x5A5A5A5A, dtype=torch.int32, device=dev())
+            ig.w8a8_sparse_i32_packed(T(X), packed, guard[1:M + 1], M, N, K)
+            assert_clean_status()
+            g = guard.cpu().numpy()
+            assert np.array_equal(g[1:M + 1], want)
+            assert (g[0] == 0x5A5A5A5A).all() and (g[-1] == 0x5A5A5A5A).all()
+            D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+            ig.w8a8_sparse_linear_packed(T(X), packed, D, T(sa), T(sw), M, N, K)
+            assert_clean_status()
+            assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
