@@ -161,6 +161,9 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the sparse / decode side measurements")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: fused = GEMM epilogue stores to all ranks over NVLink; nccl = GEMM then all-gather")
+    ap.add_argument("--workload", default="dense", choices=["dense", "sparse", "decode"],
+                    help="with --profile: which kernel to run (dense = the headline; sparse = config 3; "
+                         "decode = config 5 at M=1)")
     ap.add_argument("--profile", action="store_true",
                     help="profiler-friendly run: only warm-up + the timed steps of the headline kernel")
     args = ap.parse_args()
@@ -189,6 +192,10 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=devn)
     bm.build()
     peaks = load_peaks()
+
+    if args.profile and args.workload != "dense":
+        profile_side_workload(args, ig, oracle, torch, devn)
+        return
 
     # ---- operands: enough rotating sets that consecutive steps never hit L2 (126 MB) -------------
     n_total = N_LOCAL * world
@@ -385,6 +392,48 @@ def main() -> None:
         dist.destroy_process_group()
 
 
+def profile_side_workload(args, ig, oracle, torch, devn):
+    """Profiler-friendly run of one side workload: warm-up + steps launches of a single kernel."""
+    sid = oracle.stream_id
+    if args.workload == "sparse":
+        Ms = Ns = Ks = 4096
+        comp, nib = oracle.gen_sparse_rows(Ns, Ks, 0, sid("C3", "W"))
+        sets = 4
+        X_d = [torch.from_numpy(oracle.gen_int8((Ms, Ks), 0, sid("C3", "A"))).to(devn) for _ in range(sets)]
+        comp_d = [torch.from_numpy(comp).to(devn) for _ in range(sets)]
+        til_d = [ig.sp_pack_meta(torch.from_numpy(nib).to(devn), ig.BM_META_ROWS, Ns, Ks) for _ in range(sets)]
+        C_d = [torch.empty((Ms, Ns), dtype=torch.int32, device=devn) for _ in range(sets)]
+        fn = lambda i: ig.w8a8_sparse_i32(X_d[i % sets], comp_d[i % sets], til_d[i % sets], C_d[i % sets], Ms, Ns, Ks)
+        work = 2.0 * Ms * Ns * Ks
+        unit = "dense-equiv TOPS"
+    else:
+        Nd, Kd, Md = 28672, 8192, 1
+        comp, nib = oracle.gen_sparse_rows(Nd, Kd, 0, sid("C5", "W"))
+        comp_d = [torch.from_numpy(comp).to(devn) for _ in range(2)]
+        til_d = [ig.sp_pack_meta(torch.from_numpy(nib).to(devn), ig.BM_META_ROWS, Nd, Kd) for _ in range(2)]
+        sw = torch.from_numpy(oracle.gen_scales(Nd, 0, sid("C5", "sw"))).to(devn)
+        Xd = torch.from_numpy(oracle.gen_int8((Md, Kd), 0, sid("C5", "X1"))).to(devn)
+        sa = torch.from_numpy(oracle.gen_scales(Md, 0, sid("C5", "sa"))).to(devn)
+        Dd = torch.empty((Md, Nd), dtype=torch.float16, device=devn)
+        fn = lambda i: ig.w8a8_sparse_linear(Xd, comp_d[i % 2], til_d[i % 2], Dd, sa, sw, Md, Nd, Kd)
+        work = Nd * Kd / 2 + Nd * Kd / 8 + Md * Kd + 2 * Md * Nd + 4 * (Md + Nd)
+        unit = "GB/s"
+    torch.cuda.synchronize()                 # set-up (packing kernels) is over before the profiled launches
+    for i in range(args.warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    value = work / ms / 1e9 if args.workload == "sparse" else work / ms / 1e6
+    print(json.dumps({"profile_run": True, "workload": args.workload, "value": value, "unit": unit, "ms_per_step": ms}),
+          flush=True)
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the benchmarked kernel, from the
 # committed ncu capture (profiles/); None until one exists for this kernel build.
 TRAFFIC_BYTES_NCU = 35_935_000   # 33.663 MB read + 2.271 MB written (profiles/igemm_dense_pair_w8a8_4096_ncu_full.md)
@@ -436,7 +485,10 @@ def side_measurements(ig, oracle, torch, devn, peaks):
         byts = Nd * Kd / 2 + Nd * Kd / 8 + Md * Kd + 2 * Md * Nd + 4 * (Md + Nd)
         gbs = byts / ms / 1e6
         dec[f"M{Md}"] = {"us": ms * 1e3, "algorithmic_bytes": byts, "gb_per_s": gbs,
-                         "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+                         "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                      "frac": gbs / peaks["hbm_gbs"],
+                                      "traffic": 150_725_000 if Md == 1 else None}}
     out["decode_sparse_K8192_N28672"] = dec
     out["hbm_peak_gbs"] = peaks["hbm_gbs"]
     return out
