@@ -40,6 +40,26 @@ def build_host(force: bool = False) -> list[str]:
     return out
 
 
+COMPAT_DIR = os.path.join(PKG_DIR, "compat")
+SHIM_PATH = os.path.join(LIB_DIR, "libbm_cubin_shim.so")
+
+
+def build_shim(force: bool = False) -> str:
+    """Compile the LD_PRELOAD shim that serves the reference benches' cubin loads from libbm_igemm.so."""
+    build(force=False)
+    src = os.path.join(COMPAT_DIR, "bm_cubin_shim.cpp")
+    if force or not os.path.exists(SHIM_PATH) or os.path.getmtime(src) > os.path.getmtime(SHIM_PATH) \
+            or os.path.getmtime(LIB_PATH) > os.path.getmtime(SHIM_PATH):
+        include = os.path.join(os.path.dirname(PKG_DIR), "include")
+        cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+        cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-I" + include, "-I" + cuda_inc,
+               "-o", SHIM_PATH, src, "-L" + LIB_DIR, "-lbm_igemm", "-Wl,-rpath,$ORIGIN", "-ldl"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("building the cubin shim failed:\n" + res.stdout + res.stderr)
+    return SHIM_PATH
+
+
 def _sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh")))
 

@@ -23,6 +23,7 @@ SIGNATURES = {
     "bm_igemm_i8_f32_perchannel": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _i64, _i, _p]),
     "bm_w8a8_f16": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i64, _i, _p]),
     "bm_w8a8_f16_gather": (_i, [_p, _p, _p, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
+    "bm_quantize_rows_f16": (_i, [_p, _p, _p, _i, _i, _p]),
     "bm_pack_b_kn_to_nk": (_i, [_p, _p, _i, _i, _p]),
     "bm_sp_meta_tiled_bytes": (_sz, [_i, _i]),
     "bm_sp_pack_meta": (_i, [_p, _i, _p, _i, _i, _p]),
@@ -36,6 +37,7 @@ SIGNATURES = {
     "bm_w8a8_sparse_i32_packed": (_i, [_p, _p, _p, _i, _i, _i, _i64, _p]),
     "bm_w8a8_sparse_f16_packed": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i64, _p]),
     "bm_last_device_status": (_i, [C.POINTER(_i)]),
+    "bm_selftest_bounded_wait": (_i, [C.c_uint, C.POINTER(_i)]),
     "bm_last_error_string": (C.c_char_p, []),
     "bm_shutdown": (None, []),
     "bm_version": (C.c_char_p, []),

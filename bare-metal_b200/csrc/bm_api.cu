@@ -9,6 +9,7 @@
 #include "igemm_sparse.cuh"
 #include "igemm_sparse_pair.cuh"
 #include "pack_kernels.cuh"
+#include "quantize_kernels.cuh"
 
 namespace bm {
 
@@ -160,7 +161,6 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
     p.tiles_n = ceil_div(N, bn);
     p.k_blocks = ceil_div(K, kBK);
     p.status = dev->status;
-    if (const char* e = getenv("BM_DBG_BUF")) p.dbg_buf = reinterpret_cast<unsigned long long*>(strtoull(e, nullptr, 0));
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int grid = num_tiles < dev->sm_count ? num_tiles : dev->sm_count;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -456,6 +456,23 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
     return fail_msg(BM_ERR_SHAPE, "unsupported sparse GEMM configuration");
 }
 
+// A wait that nothing will ever satisfy, with a short limit: the give-up path of the pipeline
+// waits, exercised without hanging or faulting anything.
+__global__ void selftest_bounded_wait_kernel(int* status, unsigned long long limit_ns, int* returned) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool ok = bounded_wait(smem_u32(&bar), 0, &abort_flag, status, DEV_TIMEOUT_DRAIN, limit_ns);
+        *returned = ok ? 1 : 2;                     // 2 = gave up cleanly
+    }
+}
+
 }  // namespace bm
 
 // =========================================================================================
@@ -492,6 +509,17 @@ int bm_w8a8_f16_gather(const int8_t* X, const int8_t* W, uint16_t* const* D_peer
     if (!D_peers || n_peers <= 0) return fail_msg(BM_ERR_NULL, "no gather destinations given");
     return dense_gemm(EPI_F16_ROWCOL, X, W, D_peers[0], M, N, K, ldd, w_layout, 1.f, sa_m, sw_n, nullptr, stream,
                       reinterpret_cast<void* const*>(D_peers), n_peers);
+}
+
+int bm_quantize_rows_f16(const uint16_t* X_f16, int8_t* X_q, float* scale_m, int M, int K, void* stream) {
+    if (!X_f16 || !X_q || !scale_m) return fail_msg(BM_ERR_NULL, "pointer is NULL");
+    if (M <= 0 || K <= 0 || K % 16 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 16");
+    if (!aligned16(X_f16) || !aligned16(X_q)) return fail_msg(BM_ERR_ALIGN, "buffers must be 16-byte aligned");
+    quantize_rows_f16_kernel<<<(M + kQuantThreads / 32 - 1) / (kQuantThreads / 32), kQuantThreads, 0,
+                               static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half*>(X_f16), X_q, scale_m, M, K);
+    BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
 }
 
 int bm_pack_b_kn_to_nk(const int8_t* B_kn, int8_t* W_nk, int K, int N, void* stream) {
@@ -601,6 +629,22 @@ int bm_last_device_status(int* code) {
         // an aborted stream-K launch may have left arrival counters half-way
         if (dev->sk_counters) BM_CUDA_TRY(cudaMemset(dev->sk_counters, 0, dev->sk_counter_ints * sizeof(int)));
     }
+    return BM_OK;
+}
+
+int bm_selftest_bounded_wait(unsigned limit_us, int* outcome) {
+    if (!outcome) return fail_msg(BM_ERR_NULL, "outcome pointer is NULL");
+    if (limit_us == 0 || limit_us > 2000000u) return fail_msg(BM_ERR_SHAPE, "limit must be 1 us .. 2 s");
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    int* d_ret = nullptr;
+    BM_CUDA_TRY(cudaMalloc(&d_ret, sizeof(int)));
+    BM_CUDA_TRY(cudaMemset(d_ret, 0, sizeof(int)));
+    selftest_bounded_wait_kernel<<<1, 32>>>(dev->status, static_cast<unsigned long long>(limit_us) * 1000ull, d_ret);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(outcome, d_ret, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(d_ret);
+    if (e != cudaSuccess) return fail_cuda(e, "bounded-wait self-test");
     return BM_OK;
 }
 

@@ -62,7 +62,6 @@ struct DenseParams {
     int tail_first, tail_split;
     int* sk_counters;          // [tail tiles][2 CTAs][epilogue warps], zero between launches
     int32_t* sk_workspace;     // [tail tiles][tail_split][2 CTAs][epilogue warps][NC x 32]
-    unsigned long long* dbg_buf;   // bring-up only: per-CTA stall cycle counters (8 per CTA) when non-null
 };
 
 template <int BN, bool B_MN, int EPI>
@@ -124,15 +123,12 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             prefetch_tensormap(&map_b);
             uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
             bool ok = true;
-            long long t_wait = 0, t_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 const int m0 = (tile % p.tiles_m) * kBM;
                 const int n0 = (tile / p.tiles_m) * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    const long long tw = clock64();
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
-                    t_wait += clock64() - tw;
                     const uint32_t bar = full_bar(stage);
                     mbar_expect_tx(bar, Cfg::STAGE_BYTES);
                     tma_load_2d(a_smem0 + stage * kABytes, &map_a, bar, kb * kBK, m0);
@@ -158,7 +154,6 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                global_timer_ns() - t0 < 20000000ull) {}
                     }
             }
-            if (p.dbg_buf) { p.dbg_buf[blockIdx.x * 8 + 0] = t_wait; p.dbg_buf[blockIdx.x * 8 + 1] = clock64() - t_begin; }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -166,21 +161,16 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             constexpr uint32_t idesc = make_idesc_i8(kBM, BN, B_MN, false);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            long long t_full = 0, t_acc = 0, t_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const long long ta = clock64();
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
-                t_acc += clock64() - ta;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    const long long tf = clock64();
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
                         break;
                     }
-                    t_full += clock64() - tf;
                     tc_fence_after_sync();
                     const uint32_t a_addr = a_smem0 + stage * kABytes;
                     const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
@@ -215,10 +205,6 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 uint64_t t0 = global_timer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < 20000000ull) {}
             }
-            if (p.dbg_buf) {
-                p.dbg_buf[blockIdx.x * 8 + 2] = t_full; p.dbg_buf[blockIdx.x * 8 + 3] = t_acc;
-                p.dbg_buf[blockIdx.x * 8 + 4] = clock64() - t_begin;
-            }
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
@@ -227,7 +213,6 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         EpiStrip<Cfg::NC>* strip =
             reinterpret_cast<EpiStrip<Cfg::NC>*>(smem_gen + Cfg::STRIP_OFFSET) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
-        long long t_epi_wait = 0, t_epi_begin = clock64();
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int m0 = (tile % p.tiles_m) * kBM;
             const int n0 = (tile / p.tiles_m) * BN + half * Cfg::NC;
@@ -235,10 +220,8 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // column-side parameters of this tile, fetched while its MMAs are still running
             stage_strip<EPI, Cfg::NC, false>(p.epi, strip, n0, lane);
             const float lane_s = lane_scale_of<EPI, false>(p.epi, row);
-            const long long te = clock64();
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
-            t_epi_wait += clock64() - te;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * Cfg::NC;
             bool stored = false;
@@ -257,9 +240,6 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             if (acc == 0) acc_phase ^= 1u;
         }
         if (lane == 0) bulk_wait_all();                      // TMA stores of this warp have landed
-        if (p.dbg_buf && threadIdx.x == 64) {
-            p.dbg_buf[blockIdx.x * 8 + 5] = t_epi_wait; p.dbg_buf[blockIdx.x * 8 + 6] = clock64() - t_epi_begin;
-        }
     }
 
     // ---------------------------------------------------------------------- teardown

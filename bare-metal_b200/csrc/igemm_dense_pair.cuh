@@ -134,7 +134,6 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             prefetch_tensormap(&map_b);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            long long t_wait = 0, t_begin = clock64();
             PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
             PairWork w;
             while (ok && work.next(w)) {
@@ -142,10 +141,8 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
                 const int n0 = (tile / p.tiles_m) * kPairBN + static_cast<int>(rank) * kPairHalfN;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    const long long tw = clock64();
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
-                    t_wait += clock64() - tw;
                     const uint32_t leader_full = mapa_shared(full_bar(stage), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kPairStageBytes);
                     tma_load_2d_pair(a_smem0 + stage * kABytes, &map_a, leader_full, kb * kBK, m0);
@@ -156,7 +153,6 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (p.dbg_buf) { p.dbg_buf[blockIdx.x * 8 + 0] = t_wait; p.dbg_buf[blockIdx.x * 8 + 1] = clock64() - t_begin; }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader only)
@@ -164,23 +160,18 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             constexpr uint32_t idesc = make_idesc_i8(256, kPairBN, B_MN, false);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            long long t_full = 0, t_acc = 0, t_begin = clock64();
             PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
             PairWork w;
             while (ok && work.next(w)) {
-                const long long ta = clock64();
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
-                t_acc += clock64() - ta;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kPairBN;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    const long long tf = clock64();
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
                         break;
                     }
-                    t_full += clock64() - tf;
                     tc_fence_after_sync();
                     const uint32_t a_addr = a_smem0 + stage * kABytes;
                     const uint32_t b_addr = b_smem0 + stage * kPairBBytes;
@@ -207,10 +198,6 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 uint64_t t0 = global_timer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < 20000000ull) {}
             }
-            if (p.dbg_buf) {
-                p.dbg_buf[blockIdx.x * 8 + 2] = t_full; p.dbg_buf[blockIdx.x * 8 + 3] = t_acc;
-                p.dbg_buf[blockIdx.x * 8 + 4] = clock64() - t_begin;
-            }
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps (both CTAs)
@@ -218,7 +205,6 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int half = (warp - 2) >> 2;
         EpiStrip<kPairNC>* strip = reinterpret_cast<EpiStrip<kPairNC>*>(smem_gen + kPairStripOffset) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
-        long long t_epi_wait = 0, t_epi_begin = clock64();
         PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
         PairWork w;
         while (work.next(w)) {
@@ -228,10 +214,8 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const int row = m0 + quarter * 32 + lane;
             stage_strip<EPI, kPairNC, false>(p.epi, strip, n0, lane);
             const float lane_s = lane_scale_of<EPI, false>(p.epi, row);
-            const long long te = clock64();
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
-            t_epi_wait += clock64() - te;
             tc_fence_after_sync();
             const uint32_t taddr =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN + half * kPairNC;
@@ -281,9 +265,6 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             if (acc == 0) acc_phase ^= 1u;
         }
         if (lane == 0) bulk_wait_all();
-        if (p.dbg_buf && threadIdx.x == 64) {
-            p.dbg_buf[blockIdx.x * 8 + 5] = t_epi_wait; p.dbg_buf[blockIdx.x * 8 + 6] = clock64() - t_epi_begin;
-        }
     }
 
     // ---------------------------------------------------------------------- teardown

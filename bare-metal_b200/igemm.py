@@ -127,6 +127,19 @@ def _check_f16(D) -> bool:
     return True
 
 
+def quantize_rows(X_f16, M, K):
+    """Per-token dynamic quantisation of fp16 activations: returns (int8 [M,K], fp32 scale [M])."""
+    L = _lib.load()
+    _check_f16(X_f16)
+    if not X_f16.is_contiguous():
+        raise BmError("X must be contiguous")
+    q = torch.empty((M, K), dtype=torch.int8, device=X_f16.device)
+    s = torch.empty(M, dtype=torch.float32, device=X_f16.device)
+    _lib.check(L.bm_quantize_rows_f16(X_f16.data_ptr(), q.data_ptr(), s.data_ptr(), M, K, _stream()),
+               "bm_quantize_rows_f16")
+    return q, s
+
+
 def pack_b_kn_to_nk(B_kn, K, N):
     L = _lib.load()
     W = torch.empty((N, K), dtype=torch.int8, device=B_kn.device)

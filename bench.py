@@ -490,6 +490,14 @@ def side_measurements(ig, oracle, torch, devn, peaks):
                                       "frac": gbs / peaks["hbm_gbs"],
                                       "traffic": 150_725_000 if Md == 1 else None}}
     out["decode_sparse_K8192_N28672"] = dec
+    del comp_d, til_d
+    # the step before the path: per-token dynamic quantisation fp16 -> int8 (8192 tokens x 4096)
+    Mq, Kq = 8192, 4096
+    xs = [torch.randn((Mq, Kq), device=devn, dtype=torch.float16) for _ in range(4)]      # 4 x 64 MB > L2
+    ms = timeit(lambda i: ig.quantize_rows(xs[i % 4], Mq, Kq), 40)
+    qb = 3.0 * Mq * Kq + 4.0 * Mq
+    out["quantize_rows_8192x4096"] = {"us": ms * 1e3, "algorithmic_bytes": qb, "gb_per_s": qb / ms / 1e6,
+                                      "frac_of_hbm_peak": qb / ms / 1e6 / peaks["hbm_gbs"]}
     out["hbm_peak_gbs"] = peaks["hbm_gbs"]
     return out
 

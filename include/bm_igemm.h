@@ -85,6 +85,13 @@ int bm_w8a8_f16_gather(const int8_t *X, const int8_t *W, uint16_t *const *D_peer
                        const float *sa_m, const float *sw_n, int M, int N, int K, int64_t ldd,
                        int w_layout, void *stream);
 
+/* Per-token dynamic quantisation fp16 -> int8, the step before the W8A8 GEMM.  B200 form of the
+ * reference's online-quant kernels (igemm_online_quant.cu:144-150 take fp16 and quantise per K tile
+ * with scale = max|x|/127); here one scale per row, arithmetic of the reference's host quantiser
+ * (bench.cu:28-51): scale[m] = max|x[m][:]|/127 (1 if zero), q = clamp(roundf(x * (1/scale)), -128, 127).
+ * X_f16 is IEEE binary16 bits, row-major [M x K], K % 16 == 0. */
+int bm_quantize_rows_f16(const uint16_t *X_f16, int8_t *X_q, float *scale_m, int M, int K, void *stream);
+
 /* One-time weight repack B[K x N] -> W[N x K] (excluded from GEMM timing). */
 int bm_pack_b_kn_to_nk(const int8_t *B_kn, int8_t *W_nk, int K, int N, void *stream);
 
@@ -158,6 +165,11 @@ int bm_w8a8_sparse_f16_packed(const int8_t *X, const void *W_packed, uint16_t *D
 /* Reads (and clears) the device status word that a bounded in-kernel wait sets when it gives
  * up: *code 0 = none.  Synchronises the device. */
 int bm_last_device_status(int *code);
+/* Failure-detection self-test (no reference counterpart; the reference's persistent kernels have
+ * no watchdog): runs a one-CTA kernel that waits, with a limit of `limit_us`, on a barrier nothing
+ * signals.  *outcome = 2 when the wait gave up cleanly; bm_last_device_status then reports the
+ * recorded code (5).  The device context stays usable. */
+int bm_selftest_bounded_wait(unsigned limit_us, int *outcome);
 /* Text of the last host-side CUDA error seen by a launcher on this thread. */
 const char *bm_last_error_string(void);
 /* Frees library-owned scratch (metadata staging, status word). */

@@ -39,6 +39,9 @@ def build(force: bool = False) -> None:
     if os.path.isdir(ref_root) and (force or not os.path.exists(_REF_PATH)):
         subprocess.run(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root}"], check=True,
                        capture_output=True)
+    if os.path.isdir(ref_root) and (force or not os.path.exists(os.path.join(_HERE, "_ref", "bench"))):
+        subprocess.run(["make", "-C", _HERE, "ref_bench", f"REF_ROOT={ref_root}"], check=True,
+                       capture_output=True)
 
 
 _orc = None

@@ -202,3 +202,47 @@ def test_tail_split_of_the_last_wave(M, N, K, layout):
     C2 = torch.empty((M, N), dtype=torch.int32, device=dev())
     ig.igemm_i32(T(A), Bd, C2, M, N, K, layout)
     assert np.array_equal(C2.cpu().numpy(), acc)
+
+
+def test_bounded_wait_gives_up_with_a_status_and_the_context_survives():
+    """Failure detection without a fault: a wait nobody satisfies runs out after 2 ms, the kernel
+    returns, the status word names the wait, and the next GEMM on the same context is correct."""
+    import ctypes
+    import time
+    from bare_metal_b200 import _lib
+    L = _lib.load()
+    outcome = ctypes.c_int(0)
+    t0 = time.time()
+    assert L.bm_selftest_bounded_wait(2000, ctypes.byref(outcome)) == 0
+    assert outcome.value == 2 and time.time() - t0 < 5.0
+    assert ig.last_device_status() == 5          # DEV_TIMEOUT_DRAIN, recorded by the give-up path
+    assert ig.last_device_status() == 0          # reading clears it
+    A = oracle.gen_int8((128, 128), 1, 1)
+    B = oracle.gen_int8((128, 128), 1, 2)
+    assert np.array_equal(run_i32(A, B, ig.BM_B_NK), oracle.igemm(A, B))
+
+
+@pytest.mark.parametrize("M,K", [(64, 4096), (300, 1040), (8, 16384), (5, 16)])
+def test_per_token_quantisation_matches_the_reference_quantiser(M, K):
+    """fp16 -> int8 with one scale per row: compute_scale + quantize_symmetric of the reference's
+    bench (bench.cu:28-51) applied row by row, bit-exact; then the quantised rows feed the GEMM."""
+    rng = np.random.default_rng(M * 1000 + K)
+    x = (rng.standard_normal((M, K)) * rng.uniform(0.01, 30.0, (M, 1))).astype(np.float16)
+    x[0, :] = 0                                   # an all-zero row keeps scale 1
+    if M > 2:
+        x[2, 3] = np.float16(65504.0)             # largest finite half
+    q, s = ig.quantize_rows(T(x), M, K)
+    assert_clean_status()
+    x32 = x.astype(np.float32)
+    want_s = np.array([oracle.compute_scale(x32[m]) for m in range(M)], np.float32)
+    want_q = np.stack([oracle.quantize_symmetric(x32[m], want_s[m]) for m in range(M)])
+    assert np.array_equal(s.cpu().numpy(), want_s)
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    if K % 16 == 0 and K >= 64:
+        N = 128
+        W = oracle.gen_int8((N, K), 2, 2)
+        sw = oracle.gen_scales(N, 2, 4)
+        D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+        ig.w8a8_linear(q, T(W), D, s, T(sw), M, N, K)
+        want = oracle.dequant_w8a8_f16(oracle.igemm_nt(want_q, W), want_s, sw)
+        assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want.view(np.uint16)) <= 1

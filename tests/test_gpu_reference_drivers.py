@@ -1,0 +1,53 @@
+"""The reference project's own bench programs, UNMODIFIED (compiled from its sources in place into
+oracle/_ref by oracle/Makefile), run on top of libbm_igemm.so through the LD_PRELOAD cubin shim:
+their cuModuleLoad / cuModuleGetFunction / cuLaunchKernel calls for the INT8 GEMM kernels are served
+by the B200 launchers, and their own correctness checks and stdout contract are what is asserted."""
+import os
+import subprocess
+
+import pytest
+
+import bare_metal_b200 as bm
+from bare_metal_b200 import gate
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "oracle", "_ref")
+
+
+def run_ref(name, args, tmp_path):
+    exe = os.path.join(REF, name)
+    if not os.path.exists(exe):
+        pytest.skip("reference benches have not been built (oracle/Makefile target ref_bench)")
+    env = dict(os.environ, LD_PRELOAD=bm._build.build_shim())
+    r = subprocess.run([exe, *map(str, args)], capture_output=True, text=True, timeout=300, env=env, cwd=tmp_path)
+    return r.returncode, r.stdout.splitlines(), r.stderr
+
+
+def test_unmodified_dense_bench(tmp_path):
+    rc, out, err = run_ref("bench", [512, 512, 512], tmp_path)
+    assert rc == 0, err[-2000:]
+    text = "\n".join(out)
+    # the bench's own checks (0.5 / 0.1 AND logic against its CPU references) for every served kernel
+    for label in ("igemm_wmma", "igemm_tiled", "igemm_cpasync (LDGSTS)", "igemm_perchannel (asym)",
+                  "igemm_8warp_256 (128x256)", "igemm_persistent"):
+        lines = [ln for ln in out if label in ln and ("PASS" in ln or "FAIL" in ln)]
+        assert lines and all("PASS" in ln for ln in lines), (label, lines)
+    assert "FAIL" not in text
+    # the gate's match string for the dense kernel finds a timing line
+    p = gate.parse_throughput(out, match="igemm_cpasync")
+    assert p["ms"] is not None and p["throughput"] > 0 and p["unit"] == "TOPS"
+    # kernels outside the path (fp16 / online-quant cubins) are skipped exactly as when their cubins are absent
+    assert not any("online_quant" in ln and "ms" in ln for ln in out)
+
+
+def test_unmodified_sparse_benches(tmp_path):
+    rc, out, err = run_ref("bench_sparse", [1024, 1024, 1024], tmp_path)
+    assert rc == 0, err[-2000:]
+    assert any("igemm_sparse_tiled (INT8)" in ln and "PASS" in ln and "max_abs=0.00e+00" in ln for ln in out)
+    p = gate.parse_throughput(out, match="igemm_sparse_tiled", value_label="dense-equiv GFLOPS")
+    assert p["throughput"] > 0
+    rc, out, err = run_ref("bench_persistent", [1024, 1024, 1024], tmp_path)
+    assert rc == 0, err[-2000:]
+    p = gate.parse_throughput(out, match="igemm_sparse_tiled_persistent", value_label="eff GFLOPS")
+    assert p["throughput"] > 0
