@@ -53,10 +53,13 @@ static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const
 }
 
 // CTA-pair kernel: 2-CTA clusters, one pair per two SMs, 256 x 256 tiles
-template <bool B_MN, int EPI>
+template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
 static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& mo,
                              const DenseParams& p, int pairs, cudaStream_t stream) {
-    auto kern = igemm_dense_pair_kernel<B_MN, EPI>;
+    if constexpr (!TAIL_SPLIT) {
+        if (p.tail_split > 1) return launch_dense_pair<B_MN, EPI, true>(ma, mb, mo, p, pairs, stream);
+    }
+    auto kern = igemm_dense_pair_kernel<B_MN, EPI, TAIL_SPLIT>;
     static bool configured[kMaxDevices] = {};
     int dev = 0;
     BM_CUDA_TRY(cudaGetDevice(&dev));

@@ -72,7 +72,9 @@ struct PairWorkIter {
     }
 };
 
-template <bool B_MN, int EPI>
+// TAIL_SPLIT compiles the parked-partial-sum path in; the default instantiation leaves it out (it
+// costs registers in the drain loop even when never taken).
+template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ OutMaps maps_out, const DenseParams p) {
@@ -134,7 +136,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             prefetch_tensormap(&map_b);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
+            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1);
             PairWork w;
             while (ok && work.next(w)) {
                 const int tile = w.tile;
@@ -160,7 +162,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             constexpr uint32_t idesc = make_idesc_i8(256, kPairBN, B_MN, false);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
+            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1);
             PairWork w;
             while (ok && work.next(w)) {
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
@@ -205,7 +207,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int half = (warp - 2) >> 2;
         EpiStrip<kPairNC>* strip = reinterpret_cast<EpiStrip<kPairNC>*>(smem_gen + kPairStripOffset) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
-        PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, p.tail_split);
+        PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1);
         PairWork w;
         while (work.next(w)) {
             const int tile = w.tile;
@@ -220,7 +222,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t taddr =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN + half * kPairNC;
             const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kStoreBoxBytes;
-            if (w.part < 0) {
+            if (!TAIL_SPLIT || w.part < 0) {
                 if (p.epi.tma_ok)
                     drain_accumulator_tma<EPI, kPairNC>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
                                                         lane_s, my_stage);
@@ -229,7 +231,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
-            } else {
+            } else if constexpr (TAIL_SPLIT) {
                 // one K range of a split tail tile: park the raw sums; whoever completes the slice finishes it
                 constexpr int SLICE = kPairNC * 32;
                 const int tail_idx = tile - p.tail_first;
