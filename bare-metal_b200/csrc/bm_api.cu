@@ -271,7 +271,7 @@ static int launch_sparse_inst(const CUtensorMap& ms, const CUtensorMap& md, cons
     return BM_OK;
 }
 
-// CTA-pair kernel for sparse weights: 256 channels x 192 tokens per pair
+// CTA-pair kernel for sparse weights: 256 channels x 240 tokens per pair
 template <int EPI>
 static int launch_sparse_pair(const CUtensorMap& mw, const CUtensorMap& me, const CUtensorMap& mx, const SparseParams& p,
                               int pairs, cudaStream_t stream) {
@@ -313,9 +313,9 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
     const int tiles_r = ceil_div(R, kBM);
     int bn = forced_bn();
 
-    // large token counts with sparse weights: CTA pairs (256 channels x 192 tokens per pair)
+    // large token counts with sparse weights: CTA pairs (256 channels x 240 tokens per pair)
     if (mode == 1 && !dense_mn && !packed && sparse_pair_enabled() && dev->sm_count >= 2 &&
-        (bn == 192 || (bn == 0 && Cn >= 192 && ceil_div(R, 256) * ceil_div(Cn, kSpPairBN) >= dev->sm_count / 2))) {
+        (bn == 240 || (bn == 0 && Cn >= 192 && ceil_div(R, 256) * ceil_div(Cn, kSpPairBN) >= dev->sm_count / 2))) {
         CUtensorMap map_w, map_e, map_x;
         if (int rc = make_tensor_map_u8(&map_w, S_comp, K / 2, R, K / 2, 128, kBM, true)) return rc;
         const size_t units = meta_tiled_bytes(R, K) / 16;
@@ -343,7 +343,7 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
         if (epi == EPI_F16_ROWCOL) return launch_sparse_pair<EPI_F16_ROWCOL>(map_w, map_e, map_x, p, pairs, stream);
         return fail_msg(BM_ERR_LAYOUT, "unsupported epilogue for the sparse pair kernel");
     }
-    if (bn == 192) bn = 0;
+    if (bn == 240) bn = 0;
 
     if (bn == 0) {
         if (mode == 1) {

@@ -1,12 +1,13 @@
 // igemm_sparse_pair.cuh — 2:4-sparse WEIGHT GEMM on CTA pairs: tcgen05.mma.sp.cta_group::2.
 //
-// D^T = W_sparse * X^T with 256 output channels x 192 tokens per CTA pair.  CTA r of the pair
+// D^T = W_sparse * X^T with 256 output channels x 240 tokens per CTA pair.  CTA r of the pair
 // stages, per 256-wide K block: its 128 weight rows (kept values 128 x 128 B, TMA, 128-byte
 // swizzle), their 4 KiB of position metadata (one untiled TMA box of 256 x 16 B) and HALF of the
-// token tile (96 rows x 256 B as two swizzled boxes) — 44 KiB per stage and CTA against 84 KiB for
+// token tile (120 rows x 256 B as two swizzled boxes) — 50 KiB per stage and CTA against 84 KiB for
 // a lone CTA with a 256-token tile.  The leader's MMA lane copies the metadata of BOTH CTAs into
-// tensor memory (tcgen05.cp.cta_group::2) and issues four sparse MMAs (M = 256, N = 192, K = 64
-// logical) per stage.  Accumulators: 2 x 192 columns, metadata 8 columns per stage behind them.
+// tensor memory (tcgen05.cp.cta_group::2) and issues four sparse MMAs (M = 256, N = 240, K = 64
+// logical) per stage.  Accumulators: 2 x 240 columns, metadata 8 columns per stage behind them
+// (480 + 32 = the whole tensor memory; a 256-token tile would leave no room for the metadata).
 // Lanes are output channels, accumulator columns are tokens, so the epilogue writes D[m][n] with
 // 32 adjacent channels per warp store.  Barrier protocol as in igemm_dense_pair.cuh; no copy is
 // multicast.
@@ -18,15 +19,15 @@
 
 namespace bm {
 
-constexpr int kSpPairBN = 192;                       // tokens per pair tile (MMA N)
+constexpr int kSpPairBN = 240;                       // tokens per pair tile (MMA N): 2 x 240 + 32 = all 512 TMEM columns
 constexpr int kSpPairHalfN = kSpPairBN / 2;          // token rows staged per CTA
 constexpr int kSpPairABytes = 128 * 128;             // kept values
-constexpr int kSpPairBBytes = kSpPairHalfN * kSpKLogical;   // 24 KiB
-constexpr int kSpPairStageBytes = kSpPairABytes + kSpMetaBytes + kSpPairBBytes;   // 44 KiB
+constexpr int kSpPairBBytes = kSpPairHalfN * kSpKLogical;   // 30 KiB
+constexpr int kSpPairStageBytes = kSpPairABytes + kSpMetaBytes + kSpPairBBytes;   // 50 KiB
 constexpr int kSpPairStages = 4;
 constexpr int kSpPairEBase = 2 * kSpPairBN;          // metadata columns start after the accumulators
 constexpr int kSpPairTmemCols = 512;
-constexpr int kSpPairNC = kSpPairBN / 2;             // 96 accumulator columns per epilogue warp
+constexpr int kSpPairNC = 128;                       // accumulator columns per epilogue warp (second half: 112 live)
 constexpr int kSpPairBarOffset = kSpPairStages * kSpPairStageBytes;
 constexpr int kSpPairStripOffset = kSpPairBarOffset + (2 * kSpPairStages + 5) * 8 + 16;
 constexpr int kSpPairSmemBytes = kSpPairStripOffset + kEpiWarps * (int)sizeof(EpiStrip<kSpPairNC>) + 1024;
@@ -74,7 +75,7 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
-    const int num_tiles = p.tiles_r * p.tiles_c;        // tiles of 256 channels x 192 tokens
+    const int num_tiles = p.tiles_r * p.tiles_c;        // tiles of 256 channels x 240 tokens
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSpPairStages; ++s) {
@@ -185,7 +186,9 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         uint32_t acc = 0, acc_phase = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs) {
             const int n0 = (tile % p.tiles_r) * 256 + static_cast<int>(rank) * 128;           // first channel of this CTA
-            const int t0 = (tile / p.tiles_r) * kSpPairBN + half * kSpPairNC;                  // first token of this warp
+            const int tile_t0 = (tile / p.tiles_r) * kSpPairBN;
+            const int t0 = tile_t0 + half * kSpPairNC;                                         // first token of this warp
+            const int t_limit = p.epi.rows < tile_t0 + kSpPairBN ? p.epi.rows : tile_t0 + kSpPairBN;
             const int channel = n0 + quarter * 32 + lane;
             stage_strip<EPI, kSpPairNC, true>(p.epi, strip, t0, lane);
             const float lane_s = lane_scale_of<EPI, true>(p.epi, channel);
@@ -194,7 +197,7 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             tc_fence_after_sync();
             const uint32_t taddr =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kSpPairBN + half * kSpPairNC;
-            drain_accumulator<EPI, kSpPairNC, true>(p.epi, taddr, channel, t0, p.epi.rows, strip, lane_s);
+            drain_accumulator<EPI, kSpPairNC, true>(p.epi, taddr, channel, t0, t_limit, strip, lane_s);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));

@@ -211,15 +211,15 @@ def test_stream_k_reference_left_orientation():
     assert np.array_equal(C.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("M,N,K", [(192, 256, 256), (100, 130, 288), (400, 520, 1056), (384, 512, 4096), (1000, 1100, 544)])
+@pytest.mark.parametrize("M,N,K", [(240, 256, 256), (100, 130, 288), (400, 520, 1056), (500, 512, 4096), (1000, 1100, 544)])
 def test_sparse_weights_on_cta_pairs(M, N, K):
-    """Sparse weights on the CTA-pair kernel (tcgen05.mma.sp.cta_group::2, 256 channels x 192 tokens)."""
+    """Sparse weights on the CTA-pair kernel (tcgen05.mma.sp.cta_group::2, 256 channels x 240 tokens)."""
     comp, nib = oracle.gen_sparse_rows(N, K, 4, 51)
     X = oracle.gen_int8((M, K), 4, 52)
     want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
     tiled = ig.sp_pack_meta(T(nib), ig.BM_META_ROWS, N, K)
     guard = torch.full((M + 2, N), 0x5A5A5A5A, dtype=torch.int32, device=dev())
-    with forced_bn(192):
+    with forced_bn(240):
         ig.w8a8_sparse_i32(T(X), T(comp), tiled, guard[1:M + 1], M, N, K)
     assert_clean_status()
     g = guard.cpu().numpy()
@@ -227,7 +227,7 @@ def test_sparse_weights_on_cta_pairs(M, N, K):
     assert (g[0] == 0x5A5A5A5A).all() and (g[-1] == 0x5A5A5A5A).all()
     sa, sw = oracle.gen_scales(M, 4, 3), oracle.gen_scales(N, 4, 4)
     D = torch.zeros((M, N), dtype=torch.float16, device=dev())
-    with forced_bn(192):
+    with forced_bn(240):
         ig.w8a8_sparse_linear(T(X), T(comp), tiled, D, T(sa), T(sw), M, N, K)
     assert_clean_status()
     assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)) <= 1
