@@ -269,10 +269,13 @@ struct ParkedSource {
     __device__ __forceinline__ void wait() const {}
 };
 
-template <int EPI, int NC, class Source>
+// NBUF staging strips per warp (1 or 2), used round-robin over the boxes of all tiles (`box_count`
+// runs on across tiles).  With two strips a box is converted while the previous one is still being
+// read by its stores — what keeps the epilogue going when the stores go to other GPUs over NVLink.
+template <int EPI, int NC, int NBUF, class Source>
 __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const OutMaps& maps, int n_maps, const Source& src,
                                                int row0, int lane, int col0, const EpiStrip<NC>* strip, float lane_s,
-                                               uint32_t stage_smem) {
+                                               uint32_t stage_smem0, uint32_t& box_count) {
     using T = typename OutType<EPI>::type;
     static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
     constexpr int CHUNKS = NC / 32;
@@ -280,8 +283,8 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
     constexpr int CHUNKS_PER_BOX = COLS_PER_BOX / 32;        // 2 or 1
     constexpr int PIECES_PER_CHUNK = 32 * sizeof(T) / 16;    // 16-byte pieces a thread writes per chunk
     constexpr int PER_VEC = 16 / sizeof(T);
-    const uint32_t my_row = stage_smem + lane * 128;
     const int sw = lane & 7;                                 // 128-byte swizzle: piece index ^ (row % 8)
+    uint32_t stage_smem = stage_smem0 + (NBUF > 1 ? (box_count & 1u) * kStoreBoxBytes : 0u);
 
     uint32_t rr[2][32];
     if (col0 < p.cols) src.issue(0, rr[0]);
@@ -293,10 +296,15 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
             src.wait();
             if (c + 1 < CHUNKS && col0 + (c + 1) * 32 < p.cols) src.issue(c + 1, rr[cur ^ 1]);
             if (c % CHUNKS_PER_BOX == 0) {
-                // the strip may still be read by the previous box's store
-                if (lane == 0) bulk_wait_read_all();
+                // the strip may still be read by the store issued NBUF boxes ago
+                stage_smem = stage_smem0 + (NBUF > 1 ? (box_count & 1u) * kStoreBoxBytes : 0u);
+                if (lane == 0) {
+                    if constexpr (NBUF > 1) bulk_wait_read_all_but_one();
+                    else bulk_wait_read_all();
+                }
                 __syncwarp();
             }
+            const uint32_t my_row = stage_smem + lane * 128;
 #pragma unroll
             for (int v = 0; v < PIECES_PER_CHUNK; ++v) {
                 alignas(16) T tmp[PER_VEC];
@@ -323,15 +331,18 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
                 for (int d = 0; d < n_maps; ++d) tma_store_2d(&maps.m[d], stage_smem, box_c0, row0);
                 bulk_commit_group();
             }
+            ++box_count;
         }
     }
 }
 
-template <int EPI, int NC>
+template <int EPI, int NC, int NBUF>
 __device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const OutMaps& maps, int n_maps,
                                                       uint32_t taddr, int row0, int lane, int col0,
-                                                      const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem) {
-    drain_tma_from<EPI, NC>(p, maps, n_maps, TmemSource{taddr}, row0, lane, col0, strip, lane_s, stage_smem);
+                                                      const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem0,
+                                                      uint32_t& box_count) {
+    drain_tma_from<EPI, NC, NBUF>(p, maps, n_maps, TmemSource{taddr}, row0, lane, col0, strip, lane_s, stage_smem0,
+                                  box_count);
 }
 
 }  // namespace bm

@@ -212,7 +212,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int half = (warp - 2) >> 2;                    // which half of the tile's columns
         EpiStrip<Cfg::NC>* strip =
             reinterpret_cast<EpiStrip<Cfg::NC>*>(smem_gen + Cfg::STRIP_OFFSET) + (warp - 2);
-        uint32_t acc = 0, acc_phase = 0;
+        uint32_t acc = 0, acc_phase = 0, box_count = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int m0 = (tile % p.tiles_m) * kBM;
             const int n0 = (tile / p.tiles_m) * BN + half * Cfg::NC;
@@ -227,8 +227,9 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             bool stored = false;
             if constexpr (Cfg::NC * sizeof(typename OutType<EPI>::type) >= 128) {
                 if (p.epi.tma_ok) {
-                    drain_accumulator_tma<EPI, Cfg::NC>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip, lane_s,
-                                                        smem_base + Cfg::STORE_OFFSET + (warp - 2) * kStoreBoxBytes);
+                    drain_accumulator_tma<EPI, Cfg::NC, 1>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
+                                                           lane_s, smem_base + Cfg::STORE_OFFSET + (warp - 2) * kStoreBoxBytes,
+                                                           box_count);
                     stored = true;
                 }
             }

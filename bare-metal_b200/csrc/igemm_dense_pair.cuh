@@ -29,10 +29,11 @@ constexpr int kPairBN = 256;                       // tile columns (MMA N)
 constexpr int kPairHalfN = kPairBN / 2;            // B columns staged per CTA
 constexpr int kPairBBytes = kPairHalfN * kBK;      // 16 KiB
 constexpr int kPairStageBytes = kABytes + kPairBBytes;   // 32 KiB per CTA and stage
-constexpr int kPairStages = 5;                     // 160 KiB ring
+constexpr int kPairStages = 4;                     // 128 KiB ring
+constexpr int kPairStoreBufs = 2;                  // staging strips per epilogue warp
 constexpr int kPairTmemCols = 2 * kPairBN;         // two accumulators
 constexpr int kPairStoreOffset = kPairStages * kPairStageBytes;   // per-warp TMA-store staging
-constexpr int kPairBarOffset = kPairStoreOffset + kEpiWarps * kStoreBoxBytes;
+constexpr int kPairBarOffset = kPairStoreOffset + kEpiWarps * kPairStoreBufs * kStoreBoxBytes;
 constexpr int kPairNC = kPairBN / 2;                // columns drained per epilogue warp
 constexpr int kPairStripOffset = kPairBarOffset + (2 * kPairStages + 5) * 8 + 16;
 constexpr int kPairSmemBytes = kPairStripOffset + kEpiWarps * (int)sizeof(EpiStrip<kPairNC>) + 1024;
@@ -206,7 +207,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
         EpiStrip<kPairNC>* strip = reinterpret_cast<EpiStrip<kPairNC>*>(smem_gen + kPairStripOffset) + (warp - 2);
-        uint32_t acc = 0, acc_phase = 0;
+        uint32_t acc = 0, acc_phase = 0, box_count = 0;
         PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1);
         PairWork w;
         while (work.next(w)) {
@@ -221,11 +222,11 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             tc_fence_after_sync();
             const uint32_t taddr =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN + half * kPairNC;
-            const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kStoreBoxBytes;
+            const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kPairStoreBufs * kStoreBoxBytes;
             if (!TAIL_SPLIT || w.part < 0) {
                 if (p.epi.tma_ok)
-                    drain_accumulator_tma<EPI, kPairNC>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
-                                                        lane_s, my_stage);
+                    drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane,
+                                                                        n0, strip, lane_s, my_stage, box_count);
                 else
                     drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, p.epi.cols, strip, lane_s);
                 tc_fence_before_sync();
@@ -256,9 +257,10 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     __threadfence();
                     auto ptr = [&](int part) -> const int32_t* { return part_of(part); };
                     if (p.epi.tma_ok)
-                        drain_tma_from<EPI, kPairNC>(p.epi, maps_out, p.n_out,
-                                                     ParkedSource<decltype(ptr)>{ptr, p.tail_split, lane},
-                                                     m0 + quarter * 32, lane, n0, strip, lane_s, my_stage);
+                        drain_tma_from<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out, p.n_out,
+                                                                     ParkedSource<decltype(ptr)>{ptr, p.tail_split, lane},
+                                                                     m0 + quarter * 32, lane, n0, strip, lane_s, my_stage,
+                                                                     box_count);
                     else
                         finish_parked<EPI, kPairNC, false>(p.epi, ptr, p.tail_split, row, n0, p.epi.cols, strip, lane_s, lane);
                 }
