@@ -384,7 +384,7 @@ def main() -> None:
                                " + all-gather of the fp16 output fused into the GEMM epilogue (peer TMA stores)"
                                if args.gather == "fused" else " + NCCL all-gather of the fp16 output")),
                            "l2": f"{n_sets} rotating operand sets ({n_sets * set_bytes / 2**20:.0f} MiB) exceed the 126 MiB L2",
-                           "tile": "CTA pairs (cta_group::2), 256x256x128 per pair, 5-stage TMA ring, 2 TMEM accumulators"},
+                           "tile": "CTA pairs (cta_group::2), 256x256x128 per pair, 4-stage TMA ring, 2 TMEM accumulators"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps,
                 "clocks": clocks, "extras": extras}
         print(json.dumps(line), flush=True)
@@ -436,7 +436,7 @@ def profile_side_workload(args, ig, oracle, torch, devn):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the benchmarked kernel, from the
 # committed ncu capture (profiles/); None until one exists for this kernel build.
-TRAFFIC_BYTES_NCU = 35_935_000   # 33.663 MB read + 2.271 MB written (profiles/igemm_dense_pair_w8a8_4096_ncu_full.md)
+TRAFFIC_BYTES_NCU = 36_187_000   # 33.654 MB read + 2.532 MB written (profiles/igemm_dense_pair_w8a8_4096_ncu_full.md)
 
 
 def side_measurements(ig, oracle, torch, devn, peaks):
