@@ -54,10 +54,10 @@ static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const
 
 // CTA-pair kernel: 2-CTA clusters, one pair per two SMs, 256 x 256 tiles
 template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
-static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& mo,
+static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mbn, const OutMaps& mo,
                              const DenseParams& p, int pairs, cudaStream_t stream) {
     if constexpr (!TAIL_SPLIT) {
-        if (p.tail_split > 1) return launch_dense_pair<B_MN, EPI, true>(ma, mb, mo, p, pairs, stream);
+        if (p.tail_split > 1) return launch_dense_pair<B_MN, EPI, true>(ma, mb, mbn, mo, p, pairs, stream);
     }
     auto kern = igemm_dense_pair_kernel<B_MN, EPI, TAIL_SPLIT>;
     static bool configured[kMaxDevices] = {};
@@ -67,7 +67,7 @@ static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
         configured[dev] = true;
     }
-    BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kPairSmemBytes, stream, 2, ma, mb, mo, p));
+    BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kPairSmemBytes, stream, 2, ma, mb, mbn, mo, p));
     return BM_OK;
 }
 
@@ -107,18 +107,31 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
     const bool b_mn = (b_layout == BM_B_KN);
     const int tiles_m = ceil_div(M, kBM);
     int bn = forced_bn();
+    bool pair_ok = pair_enabled() && dev->sm_count >= 2;
     if (bn == 0) {
-        // widest tile that still gives every SM work; narrow tiles for small problems
-        const int min_bn = b_mn ? 128 : 64;
-        bn = min_bn;
-        for (int cand = 256; cand >= min_bn; cand >>= 1)
-            if (tiles_m * ceil_div(N, cand) >= dev->sm_count || cand == min_bn) { bn = cand; break; }
-        if (N <= bn / 2 && bn / 2 >= min_bn) bn /= 2;
+        // Tile choice by a wave count model: cost = start-up + waves x (time of one tile per 4096 of K).
+        // The per-wave figures (us at K = 4096, W8A8 fp16 out, one B200) were measured on problems from
+        // 64 x 512 to 4352 x 8192: narrow tiles move more operand bytes per MAC but finish a wave sooner,
+        // so they win while the wide tiles would leave SMs idle, and lose once they need a second wave.
+        struct Cand { int bn; bool pair; float wave_us, start_us; };
+        const Cand cands[4] = {{256, true, 12.0f, 3.6f}, {256, false, 12.3f, 3.0f}, {128, false, 9.8f, 2.8f},
+                               {64, false, 9.3f, 2.6f}};
+        const int min_bn = (b_mn || n_peers > 0) ? 128 : 64;
+        float best = 0.f;
+        bool best_pair = false;
+        for (const Cand& c : cands) {
+            if (c.bn < min_bn || (c.pair && !pair_ok)) continue;
+            const long long tiles = static_cast<long long>(ceil_div(M, c.pair ? 256 : kBM)) * ceil_div(N, c.bn);
+            const long long slots = c.pair ? dev->sm_count / 2 : dev->sm_count;
+            const float cost = c.start_us + static_cast<float>((tiles + slots - 1) / slots) * c.wave_us;
+            if (bn == 0 || cost < best) { best = cost; bn = c.bn; best_pair = c.pair; }
+        }
+        pair_ok = best_pair;
     }
     if (b_mn && bn < 128) bn = 128;
     if (n_peers > 0 && bn < 128) bn = 128;          // the gather rides on the TMA-store epilogue (tiles >= 128 wide)
 
-    const bool use_pair = (bn == 256) && pair_enabled() && dev->sm_count >= 2;
+    const bool use_pair = (bn == 256) && pair_ok;
 
     CUtensorMap map_a, map_b;
     if (int rc = make_tensor_map_u8(&map_a, A, K, M, K, kBK, kBM, true)) return rc;
@@ -168,6 +181,7 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
     const int grid = num_tiles < dev->sm_count ? num_tiles : dev->sm_count;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
+    CUtensorMap map_b_narrow = map_b;
     if (use_pair) {
         p.tiles_m = ceil_div(M, 256);
         const int pair_tiles = p.tiles_m * p.tiles_n;
@@ -184,6 +198,17 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
                 const int f = atoi(e);
                 if (f > 1 && f <= 4 && rem > 0 && pair_tiles > pairs && f * rem <= pairs && f <= p.k_blocks) split = f;
             }
+            // Narrow tail (default): when at most half of the pairs would work in the last wave, its tiles
+            // are computed as two 256 x 128 halves by different pairs (K-major B only; no reduction).
+            // BM_TAIL_NARROW=0 switches it off.
+            if (split == 1 && !b_mn && rem > 0 && pair_tiles > pairs && 2 * rem <= pairs) {
+                const char* e = getenv("BM_TAIL_NARROW");
+                if (!e || atoi(e) != 0) {
+                    if (int rc = make_tensor_map_u8(&map_b_narrow, B, K, N, K, kBK, 64, true)) return rc;
+                    p.tail_first = pair_tiles - rem;
+                    p.tail_narrow = 1;
+                }
+            }
             if (split > 1) {
                 const size_t slice_ints = static_cast<size_t>(kPairNC) * 32;
                 const size_t ws_bytes = static_cast<size_t>(rem) * split * 2 * kEpiWarps * slice_ints * sizeof(int32_t);
@@ -196,8 +221,8 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
         }
 #define BM_PAIR_CASE(E)                                                                         \
     case E:                                                                                     \
-        return b_mn ? launch_dense_pair<true, E>(map_a, map_b, map_out, p, pairs, stream)       \
-                    : launch_dense_pair<false, E>(map_a, map_b, map_out, p, pairs, stream);
+        return b_mn ? launch_dense_pair<true, E>(map_a, map_b, map_b_narrow, map_out, p, pairs, stream)   \
+                    : launch_dense_pair<false, E>(map_a, map_b, map_b_narrow, map_out, p, pairs, stream);
         switch (epi) {
             BM_PAIR_CASE(EPI_I32)
             BM_PAIR_CASE(EPI_F32_TENSOR)

@@ -275,7 +275,7 @@ struct ParkedSource {
 template <int EPI, int NC, int NBUF, class Source>
 __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const OutMaps& maps, int n_maps, const Source& src,
                                                int row0, int lane, int col0, const EpiStrip<NC>* strip, float lane_s,
-                                               uint32_t stage_smem0, uint32_t& box_count) {
+                                               uint32_t stage_smem0, uint32_t& box_count, int col_limit) {
     using T = typename OutType<EPI>::type;
     static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
     constexpr int CHUNKS = NC / 32;
@@ -287,14 +287,14 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
     uint32_t stage_smem = stage_smem0 + (NBUF > 1 ? (box_count & 1u) * kStoreBoxBytes : 0u);
 
     uint32_t rr[2][32];
-    if (col0 < p.cols) src.issue(0, rr[0]);
+    if (col0 < col_limit) src.issue(0, rr[0]);
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
         const int cur = c & 1;
-        const bool live = col0 + c * 32 < p.cols;            // warp-uniform
+        const bool live = col0 + c * 32 < col_limit;            // warp-uniform
         if (live) {
             src.wait();
-            if (c + 1 < CHUNKS && col0 + (c + 1) * 32 < p.cols) src.issue(c + 1, rr[cur ^ 1]);
+            if (c + 1 < CHUNKS && col0 + (c + 1) * 32 < col_limit) src.issue(c + 1, rr[cur ^ 1]);
             if (c % CHUNKS_PER_BOX == 0) {
                 // the strip may still be read by the store issued NBUF boxes ago
                 stage_smem = stage_smem0 + (NBUF > 1 ? (box_count & 1u) * kStoreBoxBytes : 0u);
@@ -324,7 +324,7 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
         }
         const bool box_done = (c % CHUNKS_PER_BOX == CHUNKS_PER_BOX - 1) || c == CHUNKS - 1;
         const int box_c0 = col0 + (c / CHUNKS_PER_BOX) * COLS_PER_BOX;
-        if (box_done && box_c0 < p.cols) {
+        if (box_done && box_c0 < col_limit) {
             fence_proxy_async_smem();                        // generic-proxy writes -> visible to the TMA engine
             __syncwarp();
             if (lane == 0) {
@@ -340,9 +340,9 @@ template <int EPI, int NC, int NBUF>
 __device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const OutMaps& maps, int n_maps,
                                                       uint32_t taddr, int row0, int lane, int col0,
                                                       const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem0,
-                                                      uint32_t& box_count) {
+                                                      uint32_t& box_count, int col_limit) {
     drain_tma_from<EPI, NC, NBUF>(p, maps, n_maps, TmemSource{taddr}, row0, lane, col0, strip, lane_s, stage_smem0,
-                                  box_count);
+                                  box_count, col_limit);
 }
 
 }  // namespace bm

@@ -60,6 +60,9 @@ struct DenseParams {
     // partly filled wave takes 1/tail_split of a tile time.  Partial sums meet in sk_workspace and
     // the part that arrives last (per epilogue warp, counted in sk_counters) finishes the tile.
     int tail_first, tail_split;
+    // narrow tail (CTA-pair kernel, K-major B): the tiles of a partly filled last wave are computed as
+    // two 256 x 128 halves by different pairs — no reduction, just smaller tiles for the idle pairs.
+    int tail_narrow;
     int* sk_counters;          // [tail tiles][2 CTAs][epilogue warps], zero between launches
     int32_t* sk_workspace;     // [tail tiles][tail_split][2 CTAs][epilogue warps][NC x 32]
 };
@@ -229,7 +232,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 if (p.epi.tma_ok) {
                     drain_accumulator_tma<EPI, Cfg::NC, 1>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
                                                            lane_s, smem_base + Cfg::STORE_OFFSET + (warp - 2) * kStoreBoxBytes,
-                                                           box_count);
+                                                           box_count, p.epi.cols);
                     stored = true;
                 }
             }

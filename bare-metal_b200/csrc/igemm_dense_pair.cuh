@@ -41,15 +41,19 @@ constexpr int kPairSmemBytes = kPairStripOffset + kEpiWarps * (int)sizeof(EpiStr
 // Work of one CTA pair: whole tiles pair, pair+P, ... below `tail_first`, then (if the tail is
 // split) one K range of one tail tile.
 struct PairWork {
-    int tile, kb0, kb1, part;           // part < 0: the whole tile
+    int tile, kb0, kb1, part;           // part < 0: the whole K range
+    int nhalf;                          // < 0: all 256 columns; 0 / 1: columns [128 nhalf, +128) only
 };
 struct PairWorkIter {
     int next_tile, pairs, tiles, tail_first, split, k_blocks, pair;
-    bool tail_done;
-    __device__ PairWorkIter(int pair_, int pairs_, int tiles_, int k_blocks_, int tail_first_, int split_)
-        : next_tile(pair_), pairs(pairs_), tiles(tiles_), tail_first(split_ > 1 ? tail_first_ : tiles_), split(split_),
-          k_blocks(k_blocks_), pair(pair_), tail_done(false) {}
+    bool tail_done, narrow;
+    __device__ PairWorkIter(int pair_, int pairs_, int tiles_, int k_blocks_, int tail_first_, int split_,
+                            bool narrow_ = false)
+        : next_tile(pair_), pairs(pairs_), tiles(tiles_),
+          tail_first((split_ > 1 || narrow_) ? tail_first_ : tiles_), split(split_), k_blocks(k_blocks_), pair(pair_),
+          tail_done(false), narrow(narrow_) {}
     __device__ bool next(PairWork& w) {
+        w.nhalf = -1;
         if (next_tile < tail_first) {
             w.tile = next_tile;
             w.kb0 = 0;
@@ -57,6 +61,18 @@ struct PairWorkIter {
             w.part = -1;
             next_tile += pairs;
             return true;
+        }
+        if (narrow && !tail_done) {
+            tail_done = true;
+            if (pair < (tiles - tail_first) * 2) {                   // pair u takes column half u % 2 of tail tile u / 2
+                w.tile = tail_first + pair / 2;
+                w.nhalf = pair % 2;
+                w.kb0 = 0;
+                w.kb1 = k_blocks;
+                w.part = -1;
+                return true;
+            }
+            return false;
         }
         if (split > 1 && !tail_done) {
             tail_done = true;
@@ -78,7 +94,8 @@ struct PairWorkIter {
 template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const __grid_constant__ OutMaps maps_out, const DenseParams p) {
+                        const __grid_constant__ CUtensorMap map_b_narrow, const __grid_constant__ OutMaps maps_out,
+                        const DenseParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -137,22 +154,26 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             prefetch_tensormap(&map_b);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1);
+            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
+                              !B_MN && p.tail_narrow != 0);
             PairWork w;
             while (ok && work.next(w)) {
                 const int tile = w.tile;
                 const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
-                const int n0 = (tile / p.tiles_m) * kPairBN + static_cast<int>(rank) * kPairHalfN;
+                const bool narrow = w.nhalf >= 0;                       // 128-column half tile: 64 B rows per CTA
+                const int n0 = (tile / p.tiles_m) * kPairBN +
+                               (narrow ? w.nhalf * 128 + static_cast<int>(rank) * 64 : static_cast<int>(rank) * kPairHalfN);
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
                     const uint32_t leader_full = mapa_shared(full_bar(stage), 0);
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), narrow ? 2 * (kABytes + 64 * kBK) : 2 * kPairStageBytes);
                     tma_load_2d_pair(a_smem0 + stage * kABytes, &map_a, leader_full, kb * kBK, m0);
                     if constexpr (B_MN)
                         tma_load_2d_pair(b_smem0 + stage * kPairBBytes, &map_b, leader_full, n0, kb * kBK);
                     else
-                        tma_load_2d_pair(b_smem0 + stage * kPairBBytes, &map_b, leader_full, kb * kBK, n0);
+                        tma_load_2d_pair(b_smem0 + stage * kPairBBytes, narrow ? &map_b_narrow : &map_b, leader_full,
+                                         kb * kBK, n0);
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -160,16 +181,19 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader only)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_i8(256, kPairBN, B_MN, false);
+            constexpr uint32_t idesc_full = make_idesc_i8(256, kPairBN, B_MN, false);
+            constexpr uint32_t idesc_narrow = make_idesc_i8(256, 128, B_MN, false);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1);
+            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
+                              !B_MN && p.tail_narrow != 0);
             PairWork w;
             while (ok && work.next(w)) {
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kPairBN;
+                const uint32_t idesc = w.nhalf >= 0 ? idesc_narrow : idesc_full;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
@@ -208,27 +232,31 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int half = (warp - 2) >> 2;
         EpiStrip<kPairNC>* strip = reinterpret_cast<EpiStrip<kPairNC>*>(smem_gen + kPairStripOffset) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0, box_count = 0;
-        PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1);
+        PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
+                              !B_MN && p.tail_narrow != 0);
         PairWork w;
         while (work.next(w)) {
             const int tile = w.tile;
             const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
-            const int n0 = (tile / p.tiles_m) * kPairBN + half * kPairNC;
+            const bool narrow = w.nhalf >= 0;                           // this warp drains 64 instead of 128 columns
+            const int n0 = (tile / p.tiles_m) * kPairBN + (narrow ? w.nhalf * 128 + half * 64 : half * kPairNC);
             const int row = m0 + quarter * 32 + lane;
+            // a narrow unit runs the same 128-column code with the column limit pulled in to 64
+            const int col_limit = narrow ? (p.epi.cols < n0 + 64 ? p.epi.cols : n0 + 64) : p.epi.cols;
             stage_strip<EPI, kPairNC, false>(p.epi, strip, n0, lane);
             const float lane_s = lane_scale_of<EPI, false>(p.epi, row);
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
             tc_fence_after_sync();
-            const uint32_t taddr =
-                tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN + half * kPairNC;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN +
+                                   (narrow ? half * 64 : half * kPairNC);
             const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kPairStoreBufs * kStoreBoxBytes;
             if (!TAIL_SPLIT || w.part < 0) {
                 if (p.epi.tma_ok)
                     drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane,
-                                                                        n0, strip, lane_s, my_stage, box_count);
+                                                                        n0, strip, lane_s, my_stage, box_count, col_limit);
                 else
-                    drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, p.epi.cols, strip, lane_s);
+                    drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, col_limit, strip, lane_s);
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
@@ -260,7 +288,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         drain_tma_from<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out, p.n_out,
                                                                      ParkedSource<decltype(ptr)>{ptr, p.tail_split, lane},
                                                                      m0 + quarter * 32, lane, n0, strip, lane_s, my_stage,
-                                                                     box_count);
+                                                                     box_count, p.epi.cols);
                     else
                         finish_parked<EPI, kPairNC, false>(p.epi, ptr, p.tail_split, row, n0, p.epi.cols, strip, lane_s, lane);
                 }

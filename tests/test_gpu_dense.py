@@ -204,6 +204,32 @@ def test_tail_split_of_the_last_wave(M, N, K, layout):
     assert np.array_equal(C2.cpu().numpy(), acc)
 
 
+@pytest.mark.parametrize("M,N,K", [(2560, 2304, 512), (2500, 2256, 272), (2500, 2250, 144), (2816, 2048, 1024)])
+def test_narrow_tiles_in_the_last_wave(M, N, K):
+    """K-major weights, more 256x256 tiles than CTA pairs and a last wave at most half full: its tiles
+    are computed as two 256x128 halves by different pairs.  Same integers as with the narrow tail
+    off, for every epilogue, ragged edges included; canary rows catch stores outside the output."""
+    from _gpu import env
+    A = oracle.gen_int8((M, K), 12, 1)
+    B = oracle.gen_int8((K, N), 12, 2)
+    acc = oracle.igemm(A, B, threads=0)
+    assert np.array_equal(run_i32(A, B, ig.BM_B_NK, guard=True), acc)
+    with env(BM_TAIL_NARROW=0):
+        assert np.array_equal(run_i32(A, B, ig.BM_B_NK, guard=True), acc)
+    Bd = T(B.T)
+    sa, sw = oracle.gen_scales(M, 12, 3), oracle.gen_scales(N, 12, 4)
+    D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+    ig.w8a8_linear(T(A), Bd, D, T(sa), T(sw), M, N, K, ig.BM_B_NK)
+    assert_clean_status()
+    want16 = oracle.dequant_w8a8_f16(acc, sa, sw).view(np.uint16)
+    assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
+    F = torch.zeros((M, N), dtype=torch.float32, device=dev())
+    ig.igemm_wmma(T(A), Bd, F, M, N, K, 0.01, 0.02, ig.BM_B_NK)
+    assert_clean_status()
+    assert np.array_equal(F.cpu().numpy().view(np.uint32), oracle.dequant_per_tensor(acc, 0.01, 0.02).view(np.uint32))
+
+
+
 def test_bounded_wait_gives_up_with_a_status_and_the_context_survives():
     """Failure detection without a fault: a wait nobody satisfies runs out after 2 ms, the kernel
     returns, the status word names the wait, and the next GEMM on the same context is correct."""
