@@ -25,6 +25,7 @@ SIGNATURES = {
     "bm_w8a8_f16_gather": (_i, [_p, _p, _p, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
     "bm_quantize_rows_f16": (_i, [_p, _p, _p, _i, _i, _p]),
     "bm_pack_b_kn_to_nk": (_i, [_p, _p, _i, _i, _p]),
+    "bm_prune_2_4_i8": (_i, [_p, _p, _p, _i, _i, _p]),
     "bm_sp_meta_tiled_bytes": (_sz, [_i, _i]),
     "bm_sp_pack_meta": (_i, [_p, _i, _p, _i, _i, _p]),
     "bm_igemm_sparse_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _p]),

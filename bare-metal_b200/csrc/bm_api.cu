@@ -550,6 +550,21 @@ int bm_quantize_rows_f16(const uint16_t* X_f16, int8_t* X_q, float* scale_m, int
     return BM_OK;
 }
 
+int bm_prune_2_4_i8(const int8_t* W, int8_t* W_comp, uint8_t* W_meta_rows, int R, int K, void* stream) {
+    if (!W || !W_comp || !W_meta_rows) return fail_msg(BM_ERR_NULL, "pointer is NULL");
+    if (R <= 0 || K <= 0 || K % 32 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 32");
+    if (!aligned16(W) || !aligned16(W_comp) || reinterpret_cast<uintptr_t>(W_meta_rows) % 4 != 0)
+        return fail_msg(BM_ERR_ALIGN, "W and W_comp must be 16-byte aligned, the metadata 4-byte aligned");
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    const size_t units = static_cast<size_t>(R) * K / 32;
+    const size_t want = (units + 255) / 256, cap = static_cast<size_t>(dev->sm_count) * 16;
+    prune_2_4_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        W, W_comp, W_meta_rows, units);
+    BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
+}
+
 int bm_pack_b_kn_to_nk(const int8_t* B_kn, int8_t* W_nk, int K, int N, void* stream) {
     if (!B_kn || !W_nk) return fail_msg(BM_ERR_NULL, "pointer is NULL");
     if (K <= 0 || N <= 0) return fail_msg(BM_ERR_SHAPE, "K and N must be positive");
@@ -699,3 +714,11 @@ void bm_shutdown(void) {
 const char* bm_version(void) { return "0.1"; }
 
 }  // extern "C"
+
+#ifdef BM_TILE_TRACE
+// developer build only: copy the pair kernel's time stamps to the host
+extern "C" int bm_debug_read_trace(void* dst, size_t bytes) {
+    if (bytes > sizeof(bm::g_pair_trace)) bytes = sizeof(bm::g_pair_trace);
+    return cudaMemcpyFromSymbol(dst, bm::g_pair_trace, bytes) == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -29,8 +29,12 @@ constexpr int kPairBN = 256;                       // tile columns (MMA N)
 constexpr int kPairHalfN = kPairBN / 2;            // B columns staged per CTA
 constexpr int kPairBBytes = kPairHalfN * kBK;      // 16 KiB
 constexpr int kPairStageBytes = kABytes + kPairBBytes;   // 32 KiB per CTA and stage
-constexpr int kPairStages = 4;                     // 128 KiB ring
-constexpr int kPairStoreBufs = 2;                  // staging strips per epilogue warp
+#ifndef BM_PAIR_STAGES
+#define BM_PAIR_STAGES 4
+#define BM_PAIR_STORE_BUFS 2
+#endif
+constexpr int kPairStages = BM_PAIR_STAGES;        // 128 KiB ring
+constexpr int kPairStoreBufs = BM_PAIR_STORE_BUFS; // staging strips per epilogue warp
 constexpr int kPairTmemCols = 2 * kPairBN;         // two accumulators
 constexpr int kPairStoreOffset = kPairStages * kPairStageBytes;   // per-warp TMA-store staging
 constexpr int kPairBarOffset = kPairStoreOffset + kEpiWarps * kPairStoreBufs * kStoreBoxBytes;
@@ -91,6 +95,17 @@ struct PairWorkIter {
 
 // TAIL_SPLIT compiles the parked-partial-sum path in; the default instantiation leaves it out (it
 // costs registers in the drain loop even when never taken).
+#ifdef BM_TILE_TRACE
+// Developer build only (-DBM_TILE_TRACE): per pair and tile, %globaltimer stamps of the MMA lane and of
+// one epilogue warp, read back with bm_debug_read_trace().
+constexpr int kTraceTiles = 8, kTraceSlots = 8;
+__device__ unsigned long long g_pair_trace[74][kTraceTiles][kTraceSlots];
+#define BM_TRACE(pair, t, slot, val) \
+    do { if ((pair) < 74 && (t) < kTraceTiles) g_pair_trace[pair][t][slot] = (val); } while (0)
+#else
+#define BM_TRACE(pair, t, slot, val) do {} while (0)
+#endif
+
 template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -188,18 +203,33 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
                               !B_MN && p.tail_narrow != 0);
             PairWork w;
+#ifdef BM_TILE_TRACE
+            int trace_t = 0;
+#endif
             while (ok && work.next(w)) {
+                BM_TRACE(pair, trace_t, 0, global_timer_ns());
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
                 tc_fence_after_sync();
+                BM_TRACE(pair, trace_t, 1, global_timer_ns());
+#ifdef BM_TILE_TRACE
+                unsigned long long wait_ns = 0;
+#endif
                 const uint32_t d_tmem = tmem_base + acc * kPairBN;
                 const uint32_t idesc = w.nhalf >= 0 ? idesc_narrow : idesc_full;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
+#ifdef BM_TILE_TRACE
+                    const unsigned long long tw0 = global_timer_ns();
+#endif
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
+#ifdef BM_TILE_TRACE
+                    if (kb == w.kb0) BM_TRACE(pair, trace_t, 2, global_timer_ns());
+                    else wait_ns += global_timer_ns() - tw0;
+#endif
                     const uint32_t a_addr = a_smem0 + stage * kABytes;
                     const uint32_t b_addr = b_smem0 + stage * kPairBBytes;
 #pragma unroll
@@ -217,6 +247,11 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (!ok) break;
                 tc_commit_pair(acc_full_bar(acc));
                 tc_commit_pair(mapa_shared(acc_full_bar(acc), 1));
+#ifdef BM_TILE_TRACE
+                BM_TRACE(pair, trace_t, 3, global_timer_ns());
+                BM_TRACE(pair, trace_t, 4, wait_ns);
+                ++trace_t;
+#endif
                 acc ^= 1u;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -235,6 +270,9 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
                               !B_MN && p.tail_narrow != 0);
         PairWork w;
+#ifdef BM_TILE_TRACE
+        int trace_e = 0;
+#endif
         while (work.next(w)) {
             const int tile = w.tile;
             const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
@@ -248,6 +286,9 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
             tc_fence_after_sync();
+#ifdef BM_TILE_TRACE
+            if (warp == 2 && lane == 0 && rank == 0) BM_TRACE(pair, trace_e, 5, global_timer_ns());
+#endif
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN +
                                    (narrow ? half * 64 : half * kPairNC);
             const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kPairStoreBufs * kStoreBoxBytes;
@@ -293,10 +334,17 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         finish_parked<EPI, kPairNC, false>(p.epi, ptr, p.tail_split, row, n0, p.epi.cols, strip, lane_s, lane);
                 }
             }
+#ifdef BM_TILE_TRACE
+            if (warp == 2 && lane == 0 && rank == 0) BM_TRACE(pair, trace_e, 6, global_timer_ns());
+            ++trace_e;
+#endif
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
         }
         if (lane == 0) bulk_wait_all();
+#ifdef BM_TILE_TRACE
+        if (warp == 2 && lane == 0 && rank == 0) BM_TRACE(pair, 0, 7, global_timer_ns());
+#endif
     }
 
     // ---------------------------------------------------------------------- teardown

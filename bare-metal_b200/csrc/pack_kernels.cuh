@@ -105,6 +105,56 @@ __global__ void pack_comp_blocks_kernel(const int8_t* __restrict__ comp, uint8_t
     *reinterpret_cast<uint4*>(packed + blk * block_stride + r * 128 + ((c ^ (r & 7)) << 4)) = v;
 }
 
+// Magnitude pruning of a dense int8 matrix W[R x K] to 2:4 along K, compression included: of every
+// aligned group of 4 the two entries of largest |w| are kept (ties: the lower position wins), written
+// lower position first into comp[R x K/2], and their positions go into the per-row nibble bytes
+// nib[R x K/8] ((idx1 << 2) | idx0; byte j = groups 2j in the low nibble, 2j + 1 in the high one) —
+// the layout compress_2_4_int8 of the reference produces for a matrix that is already 2:4
+// (kernels/gemm/igemm/sparse_meta_int8.h:137-167), with the keep mask taken from the magnitudes
+// instead of from "value != 0".  One thread per 32 input bytes: two 16-byte loads, one 16-byte store
+// of values, one 4-byte store of positions.  Streams at HBM speed: 1.625 bytes per element.
+__device__ __forceinline__ uint32_t prune_group(uint32_t word, uint32_t& kept) {
+    int a[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int v = static_cast<int8_t>((word >> (8 * i)) & 0xFFu);
+        a[i] = v < 0 ? -v : v;
+    }
+    // rank of position i = number of positions that beat it (larger |w|, or equal and lower index)
+    int idx0 = -1, idx1 = -1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int beaten_by = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) beaten_by += (j != i) && (a[j] > a[i] || (a[j] == a[i] && j < i));
+        if (beaten_by < 2) {
+            if (idx0 < 0) idx0 = i;
+            else idx1 = i;
+        }
+    }
+    kept = ((word >> (8 * idx0)) & 0xFFu) | (((word >> (8 * idx1)) & 0xFFu) << 8);
+    return (static_cast<uint32_t>(idx1) << 2) | static_cast<uint32_t>(idx0);
+}
+
+__global__ void prune_2_4_kernel(const int8_t* __restrict__ W, int8_t* __restrict__ comp, uint8_t* __restrict__ nib,
+                                 size_t units) {
+    for (size_t u = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; u < units;
+         u += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint4 lo = reinterpret_cast<const uint4*>(W)[2 * u];
+        const uint4 hi = reinterpret_cast<const uint4*>(W)[2 * u + 1];
+        const uint32_t in[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        uint32_t out[4] = {0, 0, 0, 0}, nibbles = 0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            uint32_t kept;
+            nibbles |= prune_group(in[g], kept) << (4 * g);
+            out[g >> 1] |= kept << (16 * (g & 1));
+        }
+        reinterpret_cast<uint4*>(comp)[u] = make_uint4(out[0], out[1], out[2], out[3]);
+        reinterpret_cast<uint32_t*>(nib)[u] = nibbles;
+    }
+}
+
 // B[K x N] -> W[N x K], 64 x 64 byte tiles through shared memory
 __global__ void transpose_kn_to_nk_kernel(const int8_t* __restrict__ src, int8_t* __restrict__ dst, int K, int N) {
     __shared__ int8_t tile[64][65];

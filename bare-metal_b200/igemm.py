@@ -147,6 +147,16 @@ def pack_b_kn_to_nk(B_kn, K, N):
     return W
 
 
+def prune_2_4(W, R, K):
+    """Magnitude-prune W[R,K] int8 to 2:4 along K; returns (W_comp[R,K/2] int8, meta_rows[R,K/8] uint8)."""
+    L = _lib.load()
+    comp = torch.empty((R, K // 2), dtype=torch.int8, device=W.device)
+    meta = torch.empty((R, K // 8), dtype=torch.uint8, device=W.device)
+    rc = L.bm_prune_2_4_i8(_dev(W, torch.int8, "W"), comp.data_ptr(), meta.data_ptr(), R, K, _stream())
+    _lib.check(rc, "bm_prune_2_4_i8")
+    return comp, meta
+
+
 def sp_pack_meta(meta, meta_format, R, K):
     """Re-tile 2:4 position metadata (reference uint32 words or per-row nibble bytes) once."""
     L = _lib.load()

@@ -498,6 +498,33 @@ def side_measurements(ig, oracle, torch, devn, peaks):
     qb = 3.0 * Mq * Kq + 4.0 * Mq
     out["quantize_rows_8192x4096"] = {"us": ms * 1e3, "algorithmic_bytes": qb, "gb_per_s": qb / ms / 1e6,
                                       "frac_of_hbm_peak": qb / ms / 1e6 / peaks["hbm_gbs"]}
+    del xs
+    # weight tooling: magnitude pruning to 2:4 + compression of a 28672 x 8192 int8 matrix (235 MB > L2)
+    Rp, Kp = 28672, 8192
+    Wp = torch.randint(-127, 128, (Rp, Kp), dtype=torch.int8, device=devn)
+    ms = timeit(lambda i: ig.prune_2_4(Wp, Rp, Kp), 20)
+    pb = 1.625 * Rp * Kp
+    out["prune_2to4_28672x8192"] = {"us": ms * 1e3, "algorithmic_bytes": pb, "gb_per_s": pb / ms / 1e6,
+                                    "frac_of_hbm_peak": pb / ms / 1e6 / peaks["hbm_gbs"]}
+    del Wp
+    # config 4: the four GEMMs of one 8192-token transformer layer, W8A8 -> fp16
+    Mc = 8192
+    chain = {}
+    total_ms, total_ops = 0.0, 0.0
+    for name, Kc, Nc in (("qkv", 4096, 12288), ("out", 4096, 4096), ("gate_up", 4096, 22016), ("down", 11008, 4096)):
+        Xc = torch.randint(-127, 128, (Mc, Kc), dtype=torch.int8, device=devn)
+        Wc = [torch.randint(-127, 128, (Nc, Kc), dtype=torch.int8, device=devn) for _ in range(2)]
+        sac = torch.rand(Mc, device=devn) * 0.019 + 0.001
+        swc = torch.rand(Nc, device=devn) * 0.019 + 0.001
+        Dc = torch.empty((Mc, Nc), dtype=torch.float16, device=devn)
+        ms = timeit(lambda i: ig.w8a8_linear(Xc, Wc[i % 2], Dc, sac, swc, Mc, Nc, Kc), 20)
+        ops = 2.0 * Mc * Nc * Kc
+        chain[name] = {"ms": ms, "tops": ops / ms / 1e9}
+        total_ms += ms
+        total_ops += ops
+        del Xc, Wc, Dc
+    chain["layer"] = {"ms": total_ms, "tops": total_ops / total_ms / 1e9}
+    out["layer_chain_8192_tokens"] = chain
     out["hbm_peak_gbs"] = peaks["hbm_gbs"]
     return out
 

@@ -116,6 +116,14 @@ size_t bm_sp_meta_tiled_bytes(int R, int K);
 /* one-time metadata repack (device -> device) into the kernel's tiled order */
 int bm_sp_pack_meta(const void *meta_in, int meta_format, void *meta_tiled, int R, int K, void *stream);
 
+/* Weight tooling: magnitude-prune a dense int8 matrix W[R x K] to 2:4 along K and compress it in one
+ * pass.  Of every aligned group of 4 the two entries of largest |w| stay (ties: lower position),
+ * written lower position first to W_comp[R x K/2]; positions go to W_meta_rows[R x K/8] in the
+ * BM_META_ROWS format.  For a matrix that is already 2:4 without stored zeros this is exactly what
+ * compress_2_4_int8 produces (sparse_meta_int8.h:116-178), which finds the kept entries by
+ * "value != 0"; the reference has no pruner.  K % 32 == 0. */
+int bm_prune_2_4_i8(const int8_t *W, int8_t *W_comp, uint8_t *W_meta_rows, int R, int K, void *stream);
+
 /* Replaces igemm_sparse_tiled (igemm_sparse_tiled.cu:88-96; also the _ldsm, _ldsm_fused and
  * _persistent variants minus the tile counter): sparse operand on the LEFT,
  * C[M x N] = (float)(A_sparse[M x K] * B[K x N]) * (scale_a * scale_b), metadata in the

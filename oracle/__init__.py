@@ -80,6 +80,7 @@ def lib():
         _sig(L.orc_decompress_2_4_ref, None, _p, _p, _i, _i, _p)
         _sig(L.orc_decompress_rows, None, _p, _p, _i, _i, _p)
         _sig(L.orc_meta_ref_to_rows, None, _p, _i, _i, _p)
+        _sig(L.orc_prune_2_4_rows, None, _p, _i, _i, _p, _p)
         _sig(L.orc_gen_int8_uniform, None, _p, _sz, _u64, _u64)
         _sig(L.orc_gen_f32_uniform, None, _p, _sz, _f, _f, _u64, _u64)
         _sig(L.orc_gen_sparse_rows, None, _p, _p, _i, _i, _u64, _u64)
@@ -264,6 +265,16 @@ def decompress_rows(comp: np.ndarray, nib: np.ndarray) -> np.ndarray:
     out = np.empty((R, 2 * K2), np.int8)
     lib().orc_decompress_rows(_ptr(comp), _ptr(nib), R, 2 * K2, _ptr(out))
     return out
+
+
+def prune_2_4_rows(W: np.ndarray):
+    """Magnitude pruning to 2:4 along K with compression: (comp[R,K/2] int8, nib[R,K/8] uint8)."""
+    W = np.ascontiguousarray(W, np.int8)
+    R, K = W.shape
+    comp = np.empty((R, K // 2), np.int8)
+    nib = np.empty((R, K // 8), np.uint8)
+    lib().orc_prune_2_4_rows(_ptr(W), R, K, _ptr(comp), _ptr(nib))
+    return comp, nib
 
 
 def meta_ref_to_rows(meta: np.ndarray, M: int, K: int) -> np.ndarray:

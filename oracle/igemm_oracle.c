@@ -405,6 +405,30 @@ ORC_API void orc_decompress_rows(const int8_t *comp, const uint8_t *nib, int R, 
         }
 }
 
+/* NEW (the reference has a compressor but no pruner): magnitude pruning to 2:4 with compression.
+ * Keeps the two largest |w| of every aligned group of 4 (ties: lower position), lower position first,
+ * nibble (idx1 << 2) | idx0 as compress_2_4_int8 writes it (:137-138,166-167).  On a matrix that is
+ * already 2:4 with non-zero kept values it must reproduce orc_compress_2_4_ref — tested. */
+ORC_API void orc_prune_2_4_rows(const int8_t *W, int R, int K, int8_t *comp, uint8_t *nib)
+{
+    memset(nib, 0, (size_t)R * (K / 8));
+    for (int r = 0; r < R; r++)
+        for (int g = 0; g < K / 4; g++) {
+            const int8_t *v = &W[(size_t)r * K + 4 * g];
+            int best = -1, second = -1;
+            for (int i = 0; i < 4; i++) {           /* strict > keeps the lower position on ties */
+                int a = abs((int)v[i]);
+                if (best < 0 || a > abs((int)v[best])) { second = best; best = i; }
+                else if (second < 0 || a > abs((int)v[second])) second = i;
+            }
+            int idx0 = best < second ? best : second, idx1 = best < second ? second : best;
+            comp[(size_t)r * (K / 2) + 2 * g] = v[idx0];
+            comp[(size_t)r * (K / 2) + 2 * g + 1] = v[idx1];
+            uint8_t n = (uint8_t)((idx1 << 2) | idx0);
+            nib[(size_t)r * (K / 8) + g / 2] |= (uint8_t)((g & 1) ? (n << 4) : n);
+        }
+}
+
 /* Reference metadata words -> per-row nibble bytes (rows r and r+8 share). */
 ORC_API void orc_meta_ref_to_rows(const uint32_t *meta, int M, int K, uint8_t *nib)
 {

@@ -256,3 +256,24 @@ def test_row_balanced_decode_tiles(M, N, K):
             ig.w8a8_sparse_linear_packed(T(X), packed, D, T(sa), T(sw), M, N, K)
             assert_clean_status()
             assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
+
+
+@pytest.mark.parametrize("R,K", [(16, 32), (300, 1056), (4096, 4096)])
+def test_prune_to_2_4_matches_the_oracle_and_feeds_the_sparse_gemm(R, K):
+    """Weight tooling: magnitude pruning + compression on the GPU, bit-exact against the CPU restatement,
+    then used as the sparse weights of a GEMM whose result equals the dense product of the pruned matrix."""
+    W = oracle.gen_int8((R, K), 21, 1)
+    comp_want, nib_want = oracle.prune_2_4_rows(W)
+    comp, nib = ig.prune_2_4(T(W), R, K)
+    assert np.array_equal(comp.cpu().numpy(), comp_want)
+    assert np.array_equal(nib.cpu().numpy(), nib_want)
+    if R > 1024:
+        return
+    M = 48
+    X = oracle.gen_int8((M, K), 21, 2)
+    tiled = ig.sp_pack_meta(nib, ig.BM_META_ROWS, R, K)
+    C = torch.empty((M, R), dtype=torch.int32, device=dev())
+    ig.w8a8_sparse_i32(T(X), comp, tiled, C, M, R, K)
+    assert_clean_status()
+    pruned = oracle.decompress_rows(comp_want, nib_want)
+    assert np.array_equal(C.cpu().numpy(), oracle.igemm(X, np.ascontiguousarray(pruned.T), threads=0))

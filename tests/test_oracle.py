@@ -134,3 +134,31 @@ def test_seeded_generators():
     assert len(np.unique(lo)) == 6
     dense = oracle.decompress_rows(comp, nib)
     assert ((dense.reshape(32, 64, 4) != 0).sum(axis=2) == 2).all()
+
+
+def test_prune_reproduces_the_reference_compressor_on_2_4_input():
+    """The reference has no pruner; on a matrix its own generator made 2:4 (kept values never 0,
+    sparse_meta_int8.h:91-96) pruning by magnitude must give exactly what compress_2_4_int8 gives."""
+    M, K = 64, 256
+    dense = oracle.gen_sparse_2_4_ref(M, K, 42)
+    comp_ref, meta_ref = oracle.compress_2_4_ref(dense)
+    comp, nib = oracle.prune_2_4_rows(dense)
+    assert np.array_equal(comp, comp_ref)
+    assert np.array_equal(nib, oracle.meta_ref_to_rows(meta_ref, M, K))
+    assert np.array_equal(oracle.decompress_rows(comp, nib), dense)
+
+
+def test_prune_keeps_the_two_largest_magnitudes_ties_to_the_lower_position():
+    W = np.array([[5, -5, 5, 1,   0, 0, 0, 0,   -128, 127, 3, -127,   1, 2, 3, 4] + [0] * 16], np.int8)
+    comp, nib = oracle.prune_2_4_rows(W)
+    assert comp[0, :8].tolist() == [5, -5, 0, 0, -128, 127, 3, 4]
+    assert nib[0, :2].tolist() == [(1 << 2 | 0) | ((1 << 2 | 0) << 4), (1 << 2 | 0) | ((3 << 2 | 2) << 4)]
+    rng = np.random.default_rng(5)
+    W = rng.integers(-128, 128, (48, 128), dtype=np.int8)
+    comp, nib = oracle.prune_2_4_rows(W)
+    kept = oracle.decompress_rows(comp, nib).astype(np.int32).reshape(48, 32, 4)
+    full = W.astype(np.int32).reshape(48, 32, 4)
+    # the dropped pair never outweighs the kept pair, and exactly two positions survive unless zero
+    assert (np.abs(full).sum(-1) - np.abs(kept).sum(-1) <= np.abs(kept).sum(-1)).all()
+    top2 = np.sort(np.abs(full), axis=-1)[..., 2:].sum(-1)
+    assert np.array_equal(np.abs(kept).sum(-1), top2)
