@@ -26,6 +26,8 @@ SIGNATURES = {
     "bm_quantize_rows_f16": (_i, [_p, _p, _p, _i, _i, _p]),
     "bm_pack_b_kn_to_nk": (_i, [_p, _p, _i, _i, _p]),
     "bm_prune_2_4_i8": (_i, [_p, _p, _p, _i, _i, _p]),
+    "bm_online_quant_workspace_bytes": (_sz, [_i, _i, _i]),
+    "bm_online_quant_gemm_f32": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _sz, _p]),
     "bm_sp_meta_tiled_bytes": (_sz, [_i, _i]),
     "bm_sp_pack_meta": (_i, [_p, _i, _p, _i, _i, _p]),
     "bm_igemm_sparse_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _p]),

@@ -7,7 +7,7 @@
 // INT8 GEMM kernels: the "module" and "function" handles it returns are its own records, and a launch
 // through one of them is forwarded — operands, dimensions and scales exactly as the bench passed
 // them, its grid/block geometry ignored — to the matching launcher of libbm_igemm.so.  Every other
-// driver call, and every cubin the shim does not serve (fp16 / online-quant kernels, the sm_86
+// driver call, and every cubin the shim does not serve (fp16 HGEMM kernels, the sm_86
 // hand-patched binaries), goes to the real driver untouched, so the bench skips those kernels just as
 // it does when their cubins are absent (bench.cu:98-101).
 #include <cstdint>
@@ -20,7 +20,7 @@
 
 namespace {
 
-enum Kind { DENSE, DENSE_PERSISTENT, PER_CHANNEL, SPARSE, SPARSE_PERSISTENT };
+enum Kind { DENSE, DENSE_PERSISTENT, PER_CHANNEL, SPARSE, SPARSE_PERSISTENT, ONLINE_QUANT };
 struct Served { const char* cubin; const char* symbol; Kind kind; };
 
 // cubin basename -> symbol -> argument layout (igemm.cu:52-59, igemm_persistent.cu:60-69,
@@ -38,6 +38,10 @@ const Served kServed[] = {
     {"igemm_8warp_tribuf.sm_86.cubin", "igemm_8warp_tribuf", DENSE},
     {"igemm_persistent.sm_86.cubin", "igemm_persistent", DENSE_PERSISTENT},
     {"igemm_pipelined_cpasync_perchannel.sm_86.cubin", "igemm_pipelined_cpasync_perchannel", PER_CHANNEL},
+    {"igemm_online_quant.sm_86.cubin", "igemm_online_quant", ONLINE_QUANT},                    // igemm_online_quant.cu:144-150
+    {"igemm_online_quant_inplace.sm_86.cubin", "igemm_online_quant_inplace", ONLINE_QUANT},
+    {"igemm_online_quant_bankfree.sm_86.cubin", "igemm_online_quant_bankfree", ONLINE_QUANT},
+    {"igemm_warp_specialized.sm_86.cubin", "igemm_warp_specialized", ONLINE_QUANT},
     {"igemm_sparse_tiled.sm_86.cubin", "igemm_sparse_tiled", SPARSE},
     {"igemm_sparse_tiled_persistent.sm_86.cubin", "igemm_sparse_tiled_persistent", SPARSE_PERSISTENT},
 };
@@ -153,6 +157,28 @@ CUresult cuLaunchKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, uns
                                             reinterpret_cast<const int32_t*>(arg<CUdeviceptr>(params, 7)),
                                             arg<int>(params, 4), BM_B_KN, stream);
             break;
+        case ONLINE_QUANT: {
+            // FP16 operands; the int8 copies live in a buffer the shim keeps and grows (host-side layer:
+            // the launchers themselves never allocate)
+            const int M = arg<int>(params, 3), N = arg<int>(params, 4), K = arg<int>(params, 5);
+            static CUdeviceptr ws = 0;
+            static size_t ws_bytes = 0;
+            const size_t need = bm_online_quant_workspace_bytes(M, N, K);
+            if (need > ws_bytes) {
+                auto alloc = real<CUresult (*)(CUdeviceptr*, size_t)>("cuMemAlloc_v2");
+                auto release = real<CUresult (*)(CUdeviceptr)>("cuMemFree_v2");
+                auto sync = real<CUresult (*)()>("cuCtxSynchronize");
+                if (!alloc || !release || !sync) return CUDA_ERROR_NOT_SUPPORTED;
+                if (ws) { sync(); release(ws); ws = 0; ws_bytes = 0; }
+                if (alloc(&ws, need) != CUDA_SUCCESS) return CUDA_ERROR_OUT_OF_MEMORY;
+                ws_bytes = need;
+            }
+            rc = bm_online_quant_gemm_f32(reinterpret_cast<const uint16_t*>(arg<CUdeviceptr>(params, 0)),
+                                          reinterpret_cast<const uint16_t*>(arg<CUdeviceptr>(params, 1)),
+                                          reinterpret_cast<float*>(arg<CUdeviceptr>(params, 2)), M, N, K, 128,
+                                          reinterpret_cast<void*>(ws), ws_bytes, stream);
+            break;
+        }
         case SPARSE:
         case SPARSE_PERSISTENT: {
             const int M = arg<int>(params, 4), N = arg<int>(params, 5), K = arg<int>(params, 6);

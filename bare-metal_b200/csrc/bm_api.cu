@@ -9,6 +9,7 @@
 #include "igemm_sparse.cuh"
 #include "igemm_sparse_pair.cuh"
 #include "pack_kernels.cuh"
+#include "online_quant_kernels.cuh"
 #include "quantize_kernels.cuh"
 
 namespace bm {
@@ -27,7 +28,7 @@ static int validate_epilogue(int epi, const void* out, long long ld, int cols, c
     if (!out) return fail_msg(BM_ERR_NULL, "output pointer is NULL");
     if (ld < cols) return fail_msg(BM_ERR_SHAPE, "output pitch is smaller than the row length");
     if (epi == EPI_F32_CHANNEL && (!col_scale || !col_zero)) return fail_msg(BM_ERR_NULL, "scale / zero_point is NULL");
-    if (epi == EPI_F16_ROWCOL && (!row_scale || !col_scale)) return fail_msg(BM_ERR_NULL, "row / column scale is NULL");
+    if (epi_rowcol(epi) && (!row_scale || !col_scale)) return fail_msg(BM_ERR_NULL, "row / column scale is NULL");
     return BM_OK;
 }
 
@@ -228,6 +229,9 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
             BM_PAIR_CASE(EPI_F32_TENSOR)
             BM_PAIR_CASE(EPI_F32_CHANNEL)
             BM_PAIR_CASE(EPI_F16_ROWCOL)
+            case EPI_F32_ROWCOL:                       // online-quant GEMM: B stays [K x N]
+                if (!b_mn) return fail_msg(BM_ERR_LAYOUT, "fp32 row x column scaling is built for B[K x N] only");
+                return launch_dense_pair<true, EPI_F32_ROWCOL>(map_a, map_b, map_b_narrow, map_out, p, pairs, stream);
         }
 #undef BM_PAIR_CASE
     }
@@ -241,6 +245,9 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
         BM_DENSE_CASE(EPI_F32_TENSOR)
         BM_DENSE_CASE(EPI_F32_CHANNEL)
         BM_DENSE_CASE(EPI_F16_ROWCOL)
+        case EPI_F32_ROWCOL:
+            if (!b_mn) return fail_msg(BM_ERR_LAYOUT, "fp32 row x column scaling is built for B[K x N] only");
+            return launch_dense_bn<true, EPI_F32_ROWCOL>(bn, map_a, map_b, map_out, p, grid, stream);
     }
 #undef BM_DENSE_CASE
     return fail_msg(BM_ERR_LAYOUT, "unknown epilogue");
@@ -548,6 +555,40 @@ int bm_quantize_rows_f16(const uint16_t* X_f16, int8_t* X_q, float* scale_m, int
         reinterpret_cast<const __half*>(X_f16), X_q, scale_m, M, K);
     BM_CUDA_TRY(cudaGetLastError());
     return BM_OK;
+}
+
+size_t bm_online_quant_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+    return up(static_cast<size_t>(M) * K) + up(static_cast<size_t>(K) * N) + up(sizeof(float) * M) + up(sizeof(float) * N);
+}
+
+int bm_online_quant_gemm_f32(const uint16_t* A_f16, const uint16_t* B_f16, float* C, int M, int N, int K,
+                             int col_block, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!A_f16 || !B_f16 || !C || !workspace) return fail_msg(BM_ERR_NULL, "pointer is NULL");
+    if (M <= 0 || N <= 0 || K <= 0) return fail_msg(BM_ERR_SHAPE, "M, N, K must be positive");
+    if (K % 16 != 0 || N % 16 != 0) return fail_msg(BM_ERR_SHAPE, "K and N must be multiples of 16");
+    if (col_block != 128 && col_block != 256) return fail_msg(BM_ERR_SHAPE, "column block must be 128 or 256");
+    if (!aligned16(A_f16) || !aligned16(B_f16) || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        return fail_msg(BM_ERR_ALIGN, "operands must be 16-byte aligned, the workspace 256-byte aligned");
+    if (workspace_bytes < bm_online_quant_workspace_bytes(M, N, K))
+        return fail_msg(BM_ERR_TOO_LARGE, "workspace is smaller than bm_online_quant_workspace_bytes()");
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    int8_t* Aq = reinterpret_cast<int8_t*>(ws);                 ws += up(static_cast<size_t>(M) * K);
+    int8_t* Bq = reinterpret_cast<int8_t*>(ws);                 ws += up(static_cast<size_t>(K) * N);
+    float* row_scale = reinterpret_cast<float*>(ws);            ws += up(sizeof(float) * M);
+    float* col_scale = reinterpret_cast<float*>(ws);            ws += up(sizeof(float) * N);
+    const int blocks_a = ceil_div(M, kOqRowBlock), blocks_b = ceil_div(N, col_block);
+    const int a_per = ceil_div(K, 256), b_per = ceil_div(K, kOqChunkElems / col_block);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    oq_quantize_kernel<<<blocks_a * a_per + blocks_b * b_per, kOqThreads, 0, st>>>(
+        reinterpret_cast<const __half*>(A_f16), reinterpret_cast<const __half*>(B_f16), Aq, Bq, row_scale, col_scale, M,
+        N, K, col_block, blocks_a * a_per, a_per, b_per);
+    BM_CUDA_TRY(cudaGetLastError());
+    return dense_gemm(EPI_F32_ROWCOL, Aq, Bq, C, M, N, K, N, BM_B_KN, 1.f, row_scale, col_scale, nullptr, stream);
 }
 
 int bm_prune_2_4_i8(const int8_t* W, int8_t* W_comp, uint8_t* W_meta_rows, int R, int K, void* stream) {

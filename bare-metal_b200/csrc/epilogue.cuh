@@ -10,6 +10,8 @@
 //   EPI_F32_CHANNEL  C = ((float)acc - (float)zp[n]) * scale[n]
 //                    (igemm_pipelined_cpasync_perchannel.cu:276-281)
 //   EPI_F16_ROWCOL   D = half_rn((float)acc * (sa[m] * sw[n]))
+//   EPI_F32_ROWCOL   C = (float)acc * (sa[m] * sw[n])            (online-quant GEMM: block scales
+//                    expanded per row / column, igemm_online_quant.cu:128,340-347)
 // __fmul_rn / __fsub_rn keep the compiler from contracting anything into an FMA.
 //
 // Latency structure: the parameters that vary along the accumulator COLUMNS of a tile (sw[n] and
@@ -25,7 +27,8 @@
 
 namespace bm {
 
-enum : int { EPI_I32 = 0, EPI_F32_TENSOR = 1, EPI_F32_CHANNEL = 2, EPI_F16_ROWCOL = 3 };
+enum : int { EPI_I32 = 0, EPI_F32_TENSOR = 1, EPI_F32_CHANNEL = 2, EPI_F16_ROWCOL = 3, EPI_F32_ROWCOL = 4 };
+__host__ __device__ constexpr bool epi_rowcol(int epi) { return epi == EPI_F16_ROWCOL || epi == EPI_F32_ROWCOL; }
 
 struct EpilogueParams {
     void* out;                 // C / D
@@ -58,6 +61,8 @@ convert_acc(int32_t acc, float tensor_scale, float lane_s, float cross_s, int cr
         return __fmul_rn(__int2float_rn(acc), tensor_scale);
     } else if constexpr (EPI == EPI_F32_CHANNEL) {
         return __fmul_rn(__fsub_rn(__int2float_rn(acc), __int2float_rn(cross_z)), cross_s);
+    } else if constexpr (EPI == EPI_F32_ROWCOL) {
+        return __fmul_rn(__int2float_rn(acc), __fmul_rn(lane_s, cross_s));
     } else {
         return __float2half_rn(__fmul_rn(__int2float_rn(acc), __fmul_rn(lane_s, cross_s)));
     }
@@ -73,7 +78,7 @@ struct EpiStrip {
 // Fill the strip for accumulator columns [cross0, cross0 + NC) of the coming tile.
 template <int EPI, int NC, bool TRANSPOSED>
 __device__ __forceinline__ void stage_strip(const EpilogueParams& p, EpiStrip<NC>* strip, int cross0, int lane) {
-    if constexpr (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) {
+    if constexpr (epi_rowcol(EPI) || EPI == EPI_F32_CHANNEL) {
         const float* src = TRANSPOSED ? p.row_scale : p.col_scale;
         const int limit = TRANSPOSED ? p.rows : p.cols;
 #pragma unroll
@@ -88,7 +93,7 @@ __device__ __forceinline__ void stage_strip(const EpilogueParams& p, EpiStrip<NC
 
 template <int EPI, bool TRANSPOSED>
 __device__ __forceinline__ float lane_scale_of(const EpilogueParams& p, int lane_coord) {
-    if constexpr (EPI == EPI_F16_ROWCOL) {
+    if constexpr (epi_rowcol(EPI)) {
         const float* src = TRANSPOSED ? p.col_scale : p.row_scale;
         const int limit = TRANSPOSED ? p.cols : p.rows;
         return lane_coord < limit ? __ldg(src + lane_coord) : 0.f;
@@ -113,7 +118,7 @@ __device__ __forceinline__ void emit_row_chunk(const EpilogueParams& p, int row,
             for (int j = 0; j < PER_VEC; ++j) {
                 const int k = v * PER_VEC + j;
                 tmp[j] = convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s,
-                                          (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) ? s_scale[k] : 0.f,
+                                          (epi_rowcol(EPI) || EPI == EPI_F32_CHANNEL) ? s_scale[k] : 0.f,
                                           EPI == EPI_F32_CHANNEL ? s_zero[k] : 0);
             }
             *reinterpret_cast<uint4*>(dst + v * PER_VEC) = *reinterpret_cast<const uint4*>(tmp);
@@ -123,7 +128,7 @@ __device__ __forceinline__ void emit_row_chunk(const EpilogueParams& p, int row,
         for (int k = 0; k < 32; ++k)
             if (col0 + k < p.cols)
                 dst[k] = convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s,
-                                          (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) ? s_scale[k] : 0.f,
+                                          (epi_rowcol(EPI) || EPI == EPI_F32_CHANNEL) ? s_scale[k] : 0.f,
                                           EPI == EPI_F32_CHANNEL ? s_zero[k] : 0);
     }
 }
@@ -143,7 +148,7 @@ __device__ __forceinline__ void emit_col_chunk(const EpilogueParams& p, int col,
         if (row < row_limit)
             dst[static_cast<long long>(row) * p.ld] =
                 convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s,
-                                 EPI == EPI_F16_ROWCOL ? s_scale[k] : 0.f, 0);
+                                 epi_rowcol(EPI) ? s_scale[k] : 0.f, 0);
     }
 }
 
@@ -312,7 +317,7 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
                 for (int j = 0; j < PER_VEC; ++j) {
                     const int k = v * PER_VEC + j;
                     tmp[j] = convert_acc<EPI>(static_cast<int32_t>(rr[cur][k]), p.tensor_scale, lane_s,
-                                              (EPI == EPI_F16_ROWCOL || EPI == EPI_F32_CHANNEL) ? strip->scale[c * 32 + k] : 0.f,
+                                              (epi_rowcol(EPI) || EPI == EPI_F32_CHANNEL) ? strip->scale[c * 32 + k] : 0.f,
                                               EPI == EPI_F32_CHANNEL ? strip->zero[c * 32 + k] : 0);
                 }
                 const int piece = (c % CHUNKS_PER_BOX) * PIECES_PER_CHUNK + v;

@@ -114,26 +114,18 @@ __global__ void pack_comp_blocks_kernel(const int8_t* __restrict__ comp, uint8_t
 // instead of from "value != 0".  One thread per 32 input bytes: two 16-byte loads, one 16-byte store
 // of values, one 4-byte store of positions.  Streams at HBM speed: 1.625 bytes per element.
 __device__ __forceinline__ uint32_t prune_group(uint32_t word, uint32_t& kept) {
-    int a[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int v = static_cast<int8_t>((word >> (8 * i)) & 0xFFu);
-        a[i] = v < 0 ? -v : v;
-    }
-    // rank of position i = number of positions that beat it (larger |w|, or equal and lower index)
-    int idx0 = -1, idx1 = -1;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        int beaten_by = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) beaten_by += (j != i) && (a[j] > a[i] || (a[j] == a[i] && j < i));
-        if (beaten_by < 2) {
-            if (idx0 < 0) idx0 = i;
-            else idx1 = i;
-        }
-    }
+    // key = |w| * 4 + (3 - position): distinct per position, larger key = kept first, so equal
+    // magnitudes resolve to the lower position.  __vabs4 maps -128 to 128 (no saturation).
+    const uint32_t mag = __vabs4(word);
+    const uint32_t k0 = ((mag & 0xFFu) << 2) | 3u, k1 = (((mag >> 8) & 0xFFu) << 2) | 2u;
+    const uint32_t k2 = (((mag >> 16) & 0xFFu) << 2) | 1u, k3 = ((mag >> 24) << 2);
+    const uint32_t hi01 = max(k0, k1), lo01 = min(k0, k1), hi23 = max(k2, k3), lo23 = min(k2, k3);
+    const uint32_t first = max(hi01, hi23);
+    const uint32_t second = hi01 > hi23 ? max(hi23, lo01) : max(hi01, lo23);
+    const uint32_t pa = 3u - (first & 3u), pb = 3u - (second & 3u);
+    const uint32_t idx0 = min(pa, pb), idx1 = max(pa, pb);
     kept = ((word >> (8 * idx0)) & 0xFFu) | (((word >> (8 * idx1)) & 0xFFu) << 8);
-    return (static_cast<uint32_t>(idx1) << 2) | static_cast<uint32_t>(idx0);
+    return (idx1 << 2) | idx0;
 }
 
 __global__ void prune_2_4_kernel(const int8_t* __restrict__ W, int8_t* __restrict__ comp, uint8_t* __restrict__ nib,

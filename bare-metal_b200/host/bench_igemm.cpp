@@ -12,6 +12,7 @@
 #include <cstring>
 #include <vector>
 
+#include <cuda_fp16.h>
 #include "host_common.h"
 
 static void fill_lcg(float* m, int n, unsigned seed) {            // check.h:98-106
@@ -71,6 +72,20 @@ int main(int argc, char** argv) {
     CHECK_CUDA(cudaMemcpy(dScale, pc_scale.data(), N * 4, cudaMemcpyHostToDevice));
     CHECK_CUDA(cudaMemcpy(dZp, pc_zp.data(), N * 4, cudaMemcpyHostToDevice));
 
+    // FP16 copies for the online-quant entry point (bench.cu: dev_a_fp16 / dev_b_fp16) and its workspace
+    std::vector<__half> a16(na), b16(nb);
+    for (size_t i = 0; i < na; ++i) a16[i] = __float2half(a32[i]);
+    for (size_t i = 0; i < nb; ++i) b16[i] = __float2half(b32[i]);
+    __half *dA16, *dB16;
+    void* dWs;
+    const size_t ws_bytes = bm_online_quant_workspace_bytes(M, N, K);
+    CHECK_CUDA(cudaMalloc(&dA16, na * 2)); CHECK_CUDA(cudaMalloc(&dB16, nb * 2)); CHECK_CUDA(cudaMalloc(&dWs, ws_bytes));
+    CHECK_CUDA(cudaMemcpy(dA16, a16.data(), na * 2, cudaMemcpyHostToDevice));
+    CHECK_CUDA(cudaMemcpy(dB16, b16.data(), nb * 2, cudaMemcpyHostToDevice));
+    auto online_quant = [&]() {
+        CHECK_BM(bm_online_quant_gemm_f32((const uint16_t*)dA16, (const uint16_t*)dB16, dC, M, N, K, 128, dWs, ws_bytes, nullptr));
+    };
+
     auto per_tensor = [&]() { CHECK_BM(bm_igemm_i8_f32((const int8_t*)dA, (const int8_t*)dB, dC, M, N, K, sa, sb, N, BM_B_KN, nullptr)); };
     auto per_channel = [&]() { CHECK_BM(bm_igemm_i8_f32_perchannel((const int8_t*)dA, (const int8_t*)dB, dC, M, N, K, dScale, dZp, N, BM_B_KN, nullptr)); };
 
@@ -105,6 +120,13 @@ int main(int argc, char** argv) {
         r = check_and_logic(out.data(), ref_pc.data(), (int)nc, 0.5f, 0.1f);
         print_check("igemm_perchannel (asym)", r);
         failures += r.errors;
+        CHECK_CUDA(cudaMemset(dC, 0, nc * 4));                    // bench.cu:528-541
+        online_quant();
+        CHECK_CUDA(cudaDeviceSynchronize());
+        CHECK_CUDA(cudaMemcpy(out.data(), dC, nc * 4, cudaMemcpyDeviceToHost));
+        r = check_and_logic(out.data(), ref.data(), (int)nc, 0.5f, 0.1f);
+        print_check("igemm_online_quant (FP16→INT8)", r);
+        failures += r.errors;
         printf("  Note: quantization error expected — symmetric per-tensor, scale=max_abs/127\n");
     } else {
         printf("CPU reference skipped (matrix too large — use M<=512 for correctness check)\n");
@@ -127,13 +149,22 @@ int main(int argc, char** argv) {
     run(per_tensor, "igemm_8warp_256 (128x256 cp.async)");
     run(per_tensor, "igemm_persistent (128x256 L2)");
     const double pc = run(per_channel, "igemm_perchannel (asym dequant)");
+    {                                                              // bench.cu:745-770 (GFLOPS label, FP16 in)
+        for (int i = 0; i < warmup; ++i) { CHECK_CUDA(cudaMemsetAsync(dC, 0, nc * 4, nullptr)); online_quant(); }
+        CHECK_CUDA(cudaDeviceSynchronize());
+        EventTimer t;
+        t.start();
+        for (int i = 0; i < iters; ++i) { CHECK_CUDA(cudaMemsetAsync(dC, 0, nc * 4, nullptr)); online_quant(); }
+        const float ms = t.stop_ms() / iters;
+        printf("  %-35s %7.3f ms   %8.2f GFLOPS  (FP16 in)\n", "igemm_online_quant (FP16→INT8)", ms, gemm_gops(M, N, K, ms));
+    }
     printf("  %-35s %7s      %8.0f TOPS  (theoretical, B200 dense INT8 = 4500 true TOPS)\n", "INT8 Tensor Core peak", "--", 4500000.0);
     printf("\n  Best: %.1f%% of INT8 peak\n", 100.0 * sym / 4500000.0);
     printf("  Per-channel vs symmetric: %.4f×  (%+.2f%%)\n", pc / sym, (pc / sym - 1.0) * 100.0);
     int code = 0;
     CHECK_BM(bm_last_device_status(&code));
     if (code != 0) { fprintf(stderr, "device status %d\n", code); return EXIT_FAILURE; }
-    cudaFree(dA); cudaFree(dB); cudaFree(dC); cudaFree(dScale); cudaFree(dZp);
+    cudaFree(dA); cudaFree(dB); cudaFree(dC); cudaFree(dScale); cudaFree(dZp); cudaFree(dA16); cudaFree(dB16); cudaFree(dWs);
     bm_shutdown();
     return failures ? EXIT_FAILURE : EXIT_SUCCESS;
 }

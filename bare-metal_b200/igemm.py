@@ -99,6 +99,40 @@ def igemm_sparse_tiled_persistent(A_comp, B, C, meta, M, N, K, scale_a, scale_b,
 
 
 # --------------------------------------------------------------------------------------
+# FP16-in kernels: (A_f16, B_f16, C, M, N, K) — igemm_online_quant.cu:144-150
+# --------------------------------------------------------------------------------------
+_oq_workspace = {}
+
+
+def igemm_online_quant(A, B, C, M, N, K, col_block=128, workspace=None):
+    """C[M,N] fp32 = block-quantised int8 product of fp16 A[M,K] and B[K,N]: one factor per 128-row
+    block of A and per `col_block` columns of B, taken from the first 32 of K (the reference's
+    QUANTIZE_TILE / QUANTIZE_TILE_FAST).  `workspace` (uint8 CUDA tensor) holds the int8 copies; one
+    per device is kept and grown when it is not given."""
+    L = _lib.load()
+    need = L.bm_online_quant_workspace_bytes(M, N, K)
+    if workspace is None:
+        key = A.device.index
+        workspace = _oq_workspace.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=A.device)
+            _oq_workspace[key] = workspace
+    rc = L.bm_online_quant_gemm_f32(_dev(A, torch.float16, "A"), _dev(B, torch.float16, "B"),
+                                    _dev(C, torch.float32, "C"), M, N, K, col_block,
+                                    _dev(workspace, torch.uint8, "workspace"), workspace.numel(), _stream())
+    _lib.check(rc, "bm_online_quant_gemm_f32")
+    return C
+
+
+igemm_online_quant_inplace = igemm_online_quant_bankfree = igemm_warp_specialized = igemm_online_quant
+
+
+def igemm_online_quant_bf_128x256(A, B, C, M, N, K, workspace=None):
+    """igemm_online_quant_bf_128x256.cu:258-264: 256-column blocks of B share a factor."""
+    return igemm_online_quant(A, B, C, M, N, K, 256, workspace)
+
+
+# --------------------------------------------------------------------------------------
 # entry points of the B200 workloads
 # --------------------------------------------------------------------------------------
 def igemm_i32(A, B, C, M, N, K, b_layout=BM_B_KN):

@@ -507,6 +507,14 @@ def side_measurements(ig, oracle, torch, devn, peaks):
     out["prune_2to4_28672x8192"] = {"us": ms * 1e3, "algorithmic_bytes": pb, "gb_per_s": pb / ms / 1e6,
                                     "frac_of_hbm_peak": pb / ms / 1e6 / peaks["hbm_gbs"]}
     del Wp
+    # FP16-in GEMM with the reference's per-tile quantisation: two quantising passes + block-scaled GEMM
+    Mo = No = Ko = 4096
+    Ao = [torch.rand((Mo, Ko), device=devn, dtype=torch.float16) * 2 - 1 for _ in range(3)]
+    Bo = [torch.rand((Ko, No), device=devn, dtype=torch.float16) * 2 - 1 for _ in range(3)]
+    Co = torch.empty((Mo, No), dtype=torch.float32, device=devn)
+    ms = timeit(lambda i: ig.igemm_online_quant(Ao[i % 3], Bo[i % 3], Co, Mo, No, Ko), 40)
+    out["online_quant_fp16_4096"] = {"ms": ms, "tops": 2.0 * Mo * No * Ko / ms / 1e9}
+    del Ao, Bo, Co
     # config 4: the four GEMMs of one 8192-token transformer layer, W8A8 -> fp16
     Mc = 8192
     chain = {}

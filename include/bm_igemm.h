@@ -92,6 +92,21 @@ int bm_w8a8_f16_gather(const int8_t *X, const int8_t *W, uint16_t *const *D_peer
  * X_f16 is IEEE binary16 bits, row-major [M x K], K % 16 == 0. */
 int bm_quantize_rows_f16(const uint16_t *X_f16, int8_t *X_q, float *scale_m, int M, int K, void *stream);
 
+/* Replaces igemm_online_quant (igemm_online_quant.cu:144-150) and its variants with the same
+ * arithmetic — igemm_online_quant_inplace, igemm_online_quant_bankfree, igemm_warp_specialized
+ * (col_block = 128) and igemm_online_quant_bf_128x256 (col_block = 256): FP16 operands A[M x K] and
+ * B[K x N] (IEEE binary16 bits, row-major), fp32 C[M x N] = sum over K of int8-quantised products.
+ * As in the reference each 128-row block of A and each col_block-column block of B gets ONE factor,
+ * taken from its first 32 columns / rows of K (inv = 127 / max|x|, 1 if max is 0) and applied to all
+ * of K: q = clamp(rint(x * inv), -128, 127); C = sum * ((max_a / 127) * (max_b / 127)).  The int32
+ * sums are kept exactly over all of K and scaled once, where the reference adds one fp32 product per
+ * 32-wide K tile (igemm_online_quant.cu:340-347): results agree to fp32 summation rounding.
+ * The int8 copies and the scales live in caller-owned `workspace`
+ * (>= bm_online_quant_workspace_bytes(M, N, K), 256-byte aligned).  K % 16 == 0, N % 16 == 0. */
+size_t bm_online_quant_workspace_bytes(int M, int N, int K);
+int bm_online_quant_gemm_f32(const uint16_t *A_f16, const uint16_t *B_f16, float *C, int M, int N, int K,
+                             int col_block, void *workspace, size_t workspace_bytes, void *stream);
+
 /* One-time weight repack B[K x N] -> W[N x K] (excluded from GEMM timing). */
 int bm_pack_b_kn_to_nk(const int8_t *B_kn, int8_t *W_nk, int K, int N, void *stream);
 

@@ -81,6 +81,7 @@ def lib():
         _sig(L.orc_decompress_rows, None, _p, _p, _i, _i, _p)
         _sig(L.orc_meta_ref_to_rows, None, _p, _i, _i, _p)
         _sig(L.orc_prune_2_4_rows, None, _p, _i, _i, _p, _p)
+        _sig(L.orc_online_quant_gemm, None, _p, _p, _p, _i, _i, _i, _i)
         _sig(L.orc_gen_int8_uniform, None, _p, _sz, _u64, _u64)
         _sig(L.orc_gen_f32_uniform, None, _p, _sz, _f, _f, _u64, _u64)
         _sig(L.orc_gen_sparse_rows, None, _p, _p, _i, _i, _u64, _u64)
@@ -265,6 +266,17 @@ def decompress_rows(comp: np.ndarray, nib: np.ndarray) -> np.ndarray:
     out = np.empty((R, 2 * K2), np.int8)
     lib().orc_decompress_rows(_ptr(comp), _ptr(nib), R, 2 * K2, _ptr(out))
     return out
+
+
+def online_quant_gemm(A_f16: np.ndarray, B_f16: np.ndarray, col_block: int = 128) -> np.ndarray:
+    """igemm_online_quant.cu restated: fp16 A[M,K], B[K,N] -> fp32 C[M,N] (first-tile block scales)."""
+    A = np.ascontiguousarray(A_f16, np.float16)
+    B = np.ascontiguousarray(B_f16, np.float16)
+    M, K = A.shape
+    N = B.shape[1]
+    C = np.empty((M, N), np.float32)
+    lib().orc_online_quant_gemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, col_block)
+    return C
 
 
 def prune_2_4_rows(W: np.ndarray):

@@ -497,6 +497,81 @@ ORC_API void orc_gen_sparse_rows(int8_t *comp, uint8_t *nib, int R, int K,
     }
 }
 
+/* ------------------------------------------------------------------------
+ * kernels/gemm/igemm/igemm_online_quant.cu (FP16 in, per-tile int8 quantisation, fp32 out),
+ * also _inplace, _bankfree, igemm_warp_specialized (col_block 128) and _bf_128x256 (256).
+ * Per 128 x col_block output tile (:170-173): max|A| over the tile's rows x K[0,32) and max|B|
+ * over K[0,32) x the tile's columns (QUANTIZE_TILE on tile 0, :66-98,255); inv = 127/max or 1
+ * (:100-101); every K tile is quantised with those factors (QUANTIZE_TILE_FAST, :127-142,393):
+ * q = clamp(rint(x * inv), -128, 127) (:103-116); per K tile the int32 sum is folded into an fp32
+ * running value, running += (float)acc * tile_scale (:340-347,396-433), tile_scale =
+ * (max_a/127) * (max_b/127) (:120).  nvcc contracts that update into one FMA, so fmaf here.
+ * Elements outside the matrices read as zero (:206-220).
+ * ---------------------------------------------------------------------- */
+static float half_bits_to_float(uint16_t h)
+{
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu, bits;
+    if (exp == 0) {
+        if (man == 0) bits = sign;
+        else {
+            int e = -1;
+            do { man <<= 1; e++; } while (!(man & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3FFu) << 13);
+        }
+    } else if (exp == 31) bits = sign | 0x7F800000u | (man << 13);
+    else bits = sign | ((exp + 112u) << 23) | (man << 13);
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+static int8_t oq_quant(float v, float inv)
+{
+    volatile float prod = v * inv;                 /* one fp32 multiply, no contraction */
+    long q = lrintf(prod);                         /* round to nearest even, like __float2int_rn */
+    if (q < -128) q = -128;
+    if (q > 127) q = 127;
+    return (int8_t)q;
+}
+
+ORC_API void orc_online_quant_gemm(const uint16_t *A, const uint16_t *B, float *C,
+                                   int M, int N, int K, int col_block)
+{
+    const int BMr = 128, BK = 32;
+    int blocks_a = (M + BMr - 1) / BMr, blocks_b = (N + col_block - 1) / col_block;
+    int tiles = (K + BK - 1) / BK;
+    float *max_a = (float *)calloc((size_t)blocks_a, sizeof(float));
+    float *max_b = (float *)calloc((size_t)blocks_b, sizeof(float));
+    int8_t *Aq = (int8_t *)malloc((size_t)M * K), *Bq = (int8_t *)malloc((size_t)K * N);
+    for (int m = 0; m < M; m++)
+        for (int k = 0; k < BK && k < K; k++)
+            max_a[m / BMr] = fmaxf(max_a[m / BMr], fabsf(half_bits_to_float(A[(size_t)m * K + k])));
+    for (int k = 0; k < BK && k < K; k++)
+        for (int n = 0; n < N; n++)
+            max_b[n / col_block] = fmaxf(max_b[n / col_block], fabsf(half_bits_to_float(B[(size_t)k * N + n])));
+    for (int m = 0; m < M; m++) {
+        float mx = max_a[m / BMr], inv = mx > 0.0f ? 127.0f / mx : 1.0f;
+        for (int k = 0; k < K; k++) Aq[(size_t)m * K + k] = oq_quant(half_bits_to_float(A[(size_t)m * K + k]), inv);
+    }
+    for (int n = 0; n < N; n++) {
+        float mx = max_b[n / col_block], inv = mx > 0.0f ? 127.0f / mx : 1.0f;
+        for (int k = 0; k < K; k++) Bq[(size_t)k * N + n] = oq_quant(half_bits_to_float(B[(size_t)k * N + n]), inv);
+    }
+    for (int m = 0; m < M; m++)
+        for (int n = 0; n < N; n++) {
+            float tile_scale = (max_a[m / BMr] / 127.0f) * (max_b[n / col_block] / 127.0f);
+            float running = 0.0f;
+            for (int t = 0; t < tiles; t++) {
+                int32_t acc = 0;
+                for (int k = t * BK; k < (t + 1) * BK && k < K; k++)
+                    acc += (int32_t)Aq[(size_t)m * K + k] * (int32_t)Bq[(size_t)k * N + n];
+                running = fmaf((float)acc, tile_scale, running);
+            }
+            C[(size_t)m * N + n] = running;
+        }
+    free(max_a); free(max_b); free(Aq); free(Bq);
+}
+
 /* [R x C] -> [C x R] byte transpose (layout helper for tests) */
 ORC_API void orc_transpose_i8(const int8_t *src, int8_t *dst, int R, int C)
 {

@@ -14,7 +14,9 @@ def test_dense_driver_correctness_and_stdout_contract():
     assert r["returncode"] == 0, r["err"][-2000:]
     text = "\n".join(r["out"])
     assert "igemm_cpasync (LDGSTS)" in text and "FAIL" not in text
-    assert sum("PASS" in ln for ln in r["out"]) == 2            # per-tensor and per-channel checks
+    assert sum("PASS" in ln for ln in r["out"]) == 3            # per-tensor, per-channel and FP16-in checks
+    oq = gate.parse_throughput(r["out"], match="igemm_online_quant")
+    assert oq["throughput"] > 0 and oq["unit"] == "GFLOPS"
     p = gate.parse_throughput(r["out"], match="igemm_cpasync")   # the gate's match string for the dense kernel
     assert p["ms"] is not None and p["throughput"] > 0 and p["unit"] == "TOPS"
     pc = gate.parse_throughput(r["out"], match="igemm_perchannel")

@@ -37,8 +37,15 @@ def test_unmodified_dense_bench(tmp_path):
     # the gate's match string for the dense kernel finds a timing line
     p = gate.parse_throughput(out, match="igemm_cpasync")
     assert p["ms"] is not None and p["throughput"] > 0 and p["unit"] == "TOPS"
-    # kernels outside the path (fp16 / online-quant cubins) are skipped exactly as when their cubins are absent
-    assert not any("online_quant" in ln and "ms" in ln for ln in out)
+    # the FP16-in kernels (per-tile int8 quantisation) are served too: the bench's own check against
+    # its fp32 SGEMM (bench.cu:540) and its timing lines
+    for label in ("igemm_online_quant (FP16", "igemm_inplace (FP16", "igemm_bankfree (FP16", "igemm_warpspec (FP16"):
+        lines = [ln for ln in out if label in ln and ("PASS" in ln or "FAIL" in ln)]
+        assert lines and all("PASS" in ln for ln in lines), (label, lines)
+    p = gate.parse_throughput(out, match="igemm_online_quant")
+    assert p["ms"] is not None and p["throughput"] > 0 and p["unit"] == "GFLOPS"
+    # kernels outside the path (fp16 HGEMM cubins) are skipped exactly as when their cubins are absent
+    assert not any("hgemm" in ln and " ms" in ln for ln in out)
 
 
 def test_unmodified_sparse_benches(tmp_path):

@@ -162,3 +162,28 @@ def test_prune_keeps_the_two_largest_magnitudes_ties_to_the_lower_position():
     assert (np.abs(full).sum(-1) - np.abs(kept).sum(-1) <= np.abs(kept).sum(-1)).all()
     top2 = np.sort(np.abs(full), axis=-1)[..., 2:].sum(-1)
     assert np.array_equal(np.abs(kept).sum(-1), top2)
+
+
+def test_online_quant_restatement_equals_the_reference_kernel_bit_for_bit():
+    """tests/golden/online_quant_reference.npz holds outputs of the reference's own
+    igemm_online_quant kernel (compiled unmodified for sm_100a, run on a B200 by
+    tests/golden/make_online_quant_golden.py).  The C restatement must reproduce every bit,
+    including blocks whose first K tile is all zero and values clamped by the re-used factors."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "online_quant_reference.npz"))
+    for i, (M, N, K) in enumerate(g["shapes"]):
+        A, B, C = g[f"A{i}"].view(np.float16), g[f"B{i}"].view(np.float16), g[f"C{i}"]
+        assert A.shape == (M, K) and B.shape == (K, N)
+        got = oracle.online_quant_gemm(A, B)
+        assert np.array_equal(got.view(np.uint32), C.view(np.uint32)), (M, N, K)
+    assert any((g[f"C{i}"] == 0).any() for i in range(len(g["shapes"])))      # the zero-first-tile block is in there
+
+
+def test_online_quant_256_column_blocks_share_one_factor():
+    rng = np.random.default_rng(3)
+    A = (rng.random((128, 64), dtype=np.float32) * 2 - 1).astype(np.float16)
+    B = (rng.random((64, 256), dtype=np.float32) * 2 - 1).astype(np.float16)
+    B[:32, 128:] *= np.float16(0.25)                   # right half has a smaller first-tile maximum
+    c128, c256 = oracle.online_quant_gemm(A, B, 128), oracle.online_quant_gemm(A, B, 256)
+    assert np.array_equal(c128[:, :128], c256[:, :128])            # the left block's maximum rules both
+    assert not np.array_equal(c128[:, 128:], c256[:, 128:])
