@@ -42,6 +42,10 @@ def build(force: bool = False) -> None:
     if os.path.isdir(ref_root) and (force or not os.path.exists(os.path.join(_HERE, "_ref", "bench"))):
         subprocess.run(["make", "-C", _HERE, "ref_bench", f"REF_ROOT={ref_root}"], check=True,
                        capture_output=True)
+    if os.path.isdir(ref_root) and (force or not os.path.isdir(os.path.join(_HERE, "_ref", "cubins"))):
+        # the reference's own kernels for sm_100a: GPU-side checker and "recompiled reference" baseline
+        subprocess.run(["make", "-C", _HERE, "ref_cubins", f"REF_ROOT={ref_root}"], check=True,
+                       capture_output=True)
 
 
 _orc = None

@@ -62,3 +62,47 @@ def env(**kv):
                 os.environ.pop(k, None)
             else:
                 os.environ[k] = v
+
+
+class RefKernel:
+    """One of the reference project's own kernels, compiled unmodified for sm_100a by
+    `make -C oracle ref_cubins` into oracle/_ref/cubins/<name>.sm_86.cubin (the file name its benches
+    open), loaded and launched through the CUDA driver API with the geometry its bench uses."""
+
+    def __init__(self, name):
+        import ctypes as C
+        import pytest
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "cubins",
+                            name + ".sm_86.cubin")
+        if not os.path.exists(path):
+            pytest.skip("reference kernels have not been compiled (oracle/Makefile target ref_cubins)")
+        import torch
+        torch.zeros(1, device="cuda")                         # primary context current on this thread
+        self.C = C
+        self.cu = C.CDLL("libcuda.so.1")
+        self.mod, self.fn = C.c_void_p(), C.c_void_p()
+        self._ck(self.cu.cuModuleLoad(C.byref(self.mod), path.encode()), "cuModuleLoad")
+        self._ck(self.cu.cuModuleGetFunction(C.byref(self.fn), self.mod, name.encode()), "cuModuleGetFunction")
+
+    @staticmethod
+    def _ck(rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what} failed with CUresult {rc}")
+
+    def launch(self, grid, block, args):
+        """args: torch tensors (passed as device pointers), python ints (int) and floats (float)."""
+        import torch
+        C = self.C
+        keep = []
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                keep.append(C.c_void_p(a.data_ptr()))
+            elif isinstance(a, float):
+                keep.append(C.c_float(a))
+            else:
+                keep.append(C.c_int(int(a)))
+        params = (C.c_void_p * len(keep))(*[C.cast(C.byref(x), C.c_void_p) for x in keep])
+        torch.cuda.synchronize()
+        self._ck(self.cu.cuLaunchKernel(self.fn, grid[0], grid[1], 1, block[0], block[1], 1, 0, None, params, None),
+                 "cuLaunchKernel")
+        self._ck(self.cu.cuCtxSynchronize(), "cuCtxSynchronize")

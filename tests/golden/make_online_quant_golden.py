@@ -2,7 +2,7 @@
 
 Runs on a machine with a GPU.  `make -C oracle ref_cubins` (on a machine that has the reference
 checkout) compiles kernels/gemm/igemm/igemm_online_quant.cu, unmodified, to
-oracle/_ref/igemm_online_quant.sm_100a.cubin; this script loads that cubin through the CUDA driver
+oracle/_ref/cubins/igemm_online_quant.sm_86.cubin (the file name the reference bench opens; sm_100a code); this script loads that cubin through the CUDA driver
 API, launches `igemm_online_quant` with the geometry the reference bench uses
 (bench.cu:529-536: grid ((N+127)/128, (M+127)/128), block 256, no dynamic shared memory) on seeded
 inputs and stores inputs and outputs in tests/golden/online_quant_reference.npz.  The CPU tests
@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-CUBIN = os.path.join(ROOT, "oracle", "_ref", "igemm_online_quant.sm_100a.cubin")
+CUBIN = os.path.join(ROOT, "oracle", "_ref", "cubins", "igemm_online_quant.sm_86.cubin")
 
 # sizes inside the domain the reference bench exercises: M, N multiples of 128, K of 32
 CASES = [(128, 128, 64, 1), (256, 384, 160, 2), (256, 256, 512, 3)]

@@ -58,3 +58,23 @@ def test_unmodified_sparse_benches(tmp_path):
     assert rc == 0, err[-2000:]
     p = gate.parse_throughput(out, match="igemm_sparse_tiled_persistent", value_label="eff GFLOPS")
     assert p["throughput"] > 0
+
+
+def test_reference_kernels_recompiled_for_sm100a_are_the_baseline_we_beat(tmp_path):
+    """The same unmodified bench binary twice at 4096^3: once loading the reference's own kernels
+    (compiled for sm_100a into oracle/_ref/cubins), once served by this library through the shim.
+    Both pass on a B200; the library has to be at least 10x faster on the gate's dense line."""
+    cubins = os.path.join(REF, "cubins")
+    exe = os.path.join(REF, "bench")
+    if not os.path.isdir(cubins) or not os.path.exists(exe):
+        pytest.skip("reference kernels / benches have not been built (oracle/Makefile ref_cubins, ref_bench)")
+    r = subprocess.run([exe, "4096", "4096", "4096"], capture_output=True, text=True, timeout=600, cwd=cubins)
+    assert r.returncode == 0, r.stderr[-2000:]
+    theirs = gate.parse_throughput(r.stdout.splitlines(), match="igemm_cpasync")
+    rc, out, err = run_ref("bench", [4096, 4096, 4096], tmp_path)
+    assert rc == 0, err[-2000:]
+    ours = gate.parse_throughput(out, match="igemm_cpasync")
+    assert theirs["throughput"] > 0 and ours["throughput"] > 10 * theirs["throughput"], (theirs, ours)
+    their_oq = gate.parse_throughput(r.stdout.splitlines(), match="igemm_online_quant")
+    our_oq = gate.parse_throughput(out, match="igemm_online_quant")
+    assert our_oq["throughput"] > 10 * their_oq["throughput"], (their_oq, our_oq)
