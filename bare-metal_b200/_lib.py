@@ -32,6 +32,7 @@ SIGNATURES = {
     "bm_sp_pack_meta": (_i, [_p, _i, _p, _i, _i, _p]),
     "bm_igemm_sparse_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _p]),
     "bm_igemm_sparse_f32_noalloc": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _p]),
+    "bm_hgemm_sparse_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i64, _p]),
     "bm_igemm_sparse_i32": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
     "bm_w8a8_sparse_i32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i64, _p]),
     "bm_w8a8_sparse_f16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i64, _p]),
@@ -47,7 +48,7 @@ SIGNATURES = {
 }
 
 BM_B_KN, BM_B_NK = 0, 1
-BM_META_REF, BM_META_ROWS, BM_META_TILED = 0, 1, 2
+BM_META_REF, BM_META_ROWS, BM_META_TILED, BM_META_REF_F16, BM_META_ROWS_F16 = 0, 1, 2, 3, 4
 
 _lib = None
 

@@ -263,21 +263,27 @@ static size_t meta_tiled_bytes(int R, int K) {
 static int pack_meta(const void* meta_in, int fmt, void* tiled, int R, int K, cudaStream_t stream,
                      size_t block_stride = kSpMetaBytes, size_t block_offset = 0) {
     if (!meta_in || !tiled) return fail_msg(BM_ERR_NULL, "metadata pointer is NULL");
-    if (R <= 0 || K <= 0 || K % 32 != 0) return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 32");
-    if (fmt == BM_META_REF && R % 16 != 0) return fail_msg(BM_ERR_SHAPE, "reference metadata needs rows % 16 == 0");
+    if (R <= 0 || K <= 0 || K % (fmt == BM_META_REF_F16 ? 16 : 32) != 0)
+        return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 32 (16 for the fp16 reference format)");
+    if ((fmt == BM_META_REF || fmt == BM_META_REF_F16) && R % 16 != 0)
+        return fail_msg(BM_ERR_SHAPE, "reference metadata needs rows % 16 == 0");
     if (!aligned16(tiled) || (reinterpret_cast<uintptr_t>(meta_in) & 3u))
         return fail_msg(BM_ERR_ALIGN, "metadata buffers are misaligned");
     const int k_blocks = ceil_div(K, kSpKLogical);
     const size_t units = meta_tiled_bytes(R, K) / 16;
     const unsigned blocks = static_cast<unsigned>((units + 255) / 256);
-    if (fmt == BM_META_ROWS)
+    if (fmt == BM_META_ROWS || fmt == BM_META_ROWS_F16)
         pack_meta_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(meta_in),
                                                           static_cast<uint8_t*>(tiled), R, K, k_blocks, units,
-                                                          block_stride, block_offset);
+                                                          block_stride, block_offset, fmt == BM_META_ROWS_F16 ? 1 : 0);
     else if (fmt == BM_META_REF)
         pack_meta_ref_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(meta_in),
                                                          static_cast<uint8_t*>(tiled), R, K, k_blocks, units,
                                                          block_stride, block_offset);
+    else if (fmt == BM_META_REF_F16)
+        pack_meta_ref_f16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(meta_in),
+                                                             static_cast<uint8_t*>(tiled), R, K, k_blocks, units,
+                                                             block_stride, block_offset);
     else if (fmt == BM_META_TILED && block_stride != kSpMetaBytes)
         pack_meta_copy_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(meta_in),
                                                           static_cast<uint8_t*>(tiled), units, block_stride, block_offset);
@@ -515,6 +521,23 @@ __global__ void selftest_bounded_wait_kernel(int* status, unsigned long long lim
 // =========================================================================================
 using namespace bm;
 
+// FP16 2:4 GEMM (kernels/gemm/hgemm_sparse): the sparse kernel in its fp16 form, one CTA per tile
+template <int BN>
+static int launch_hsparse(const CUtensorMap& ms, const CUtensorMap& md, const SparseParams& p, int grid,
+                          cudaStream_t stream) {
+    using Cfg = SparseCfg<BN>;
+    auto kern = igemm_sparse_kernel<BN, true, false, EPI_I32, false, true>;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    BM_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev]) {
+        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured[dev] = true;
+    }
+    BM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, 1, ms, md, p));
+    return BM_OK;
+}
+
 extern "C" {
 
 int bm_igemm_i8_i32(const int8_t* A, const int8_t* B, int32_t* C, int M, int N, int K, int64_t ldc, int b_layout,
@@ -647,6 +670,44 @@ int bm_igemm_sparse_f32(const int8_t* A_comp, const int8_t* B, float* C, const u
     if (int rc = resolve_meta(meta, BM_META_REF, M, K, stream, &tiled)) return rc;
     volatile float dequant = scale_a * scale_b;       // igemm_sparse_tiled.cu:365
     return sparse_gemm(0, EPI_F32_TENSOR, A_comp, tiled, B, C, M, N, K, N, BM_B_KN, dequant, nullptr, nullptr, stream);
+}
+
+int bm_hgemm_sparse_f32(const uint16_t* A_comp, const uint16_t* B, float* C, const void* meta, int meta_format,
+                        int M, int N, int K, int64_t ldc, void* stream_v) {
+    if (!A_comp || !B || !C || !meta) return fail_msg(BM_ERR_NULL, "pointer is NULL");
+    if (M <= 0 || N <= 0 || K <= 0) return fail_msg(BM_ERR_SHAPE, "dimensions must be positive");
+    if (K % 16 != 0 || N % 16 != 0) return fail_msg(BM_ERR_SHAPE, "K and N must be multiples of 16");
+    if (ldc < N) return fail_msg(BM_ERR_SHAPE, "output pitch is smaller than the row length");
+    if (!aligned16(A_comp) || !aligned16(B)) return fail_msg(BM_ERR_ALIGN, "operands must be 16-byte aligned");
+    if (meta_format == BM_META_REF) return fail_msg(BM_ERR_LAYOUT, "the int8 reference metadata format does not describe fp16 operands");
+    if (meta_format == BM_META_ROWS) meta_format = BM_META_ROWS_F16;      // per-row bytes, tiled in the fp16 lane order
+    const uint8_t* tiled = nullptr;
+    if (int rc = resolve_meta(meta, meta_format, M, K, stream_v, &tiled)) return rc;
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    const int tiles_r = ceil_div(M, kBM);
+    int bn = forced_bn();
+    if (bn != 128 && bn != 256) bn = (static_cast<long long>(tiles_r) * ceil_div(N, 256) >= dev->sm_count) ? 256 : 128;
+    CUtensorMap map_s, map_d;        // byte maps: compressed A is [M x K bytes], B is [K x 2N bytes]
+    if (int rc = make_tensor_map_u8(&map_s, A_comp, K, M, K, 128, kBM, true)) return rc;
+    if (int rc = make_tensor_map_u8(&map_d, B, 2 * static_cast<size_t>(N), K, 2 * static_cast<size_t>(N), 128, 128, true))
+        return rc;
+    SparseParams p{};
+    p.epi.out = C;                   // fp32 accumulator bits are stored as they are (EPI_I32)
+    p.epi.ld = ldc;
+    p.epi.rows = M;
+    p.epi.cols = N;
+    p.epi.vec_ok = aligned16(C) && (static_cast<size_t>(ldc) * 4) % 16 == 0;
+    p.meta_tiled = tiled;
+    p.tiles_r = tiles_r;
+    p.tiles_c = ceil_div(N, bn);
+    p.k_blocks = ceil_div(K, 128);
+    p.status = dev->status;
+    p.sparse_rows = M;
+    const int num_tiles = p.tiles_r * p.tiles_c;
+    const int grid = num_tiles < dev->sm_count ? num_tiles : dev->sm_count;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    return bn == 256 ? launch_hsparse<256>(map_s, map_d, p, grid, stream) : launch_hsparse<128>(map_s, map_d, p, grid, stream);
 }
 
 int bm_igemm_sparse_i32(const int8_t* A_comp, const void* meta, int meta_format, const int8_t* B, int32_t* C, int M,

@@ -142,12 +142,23 @@ __device__ __forceinline__ int stream_k_owner(long long u, long long U, int ctas
     return static_cast<int>(((u + 1) * ctas - 1) / U);
 }
 
-template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false>
+// F16 = true turns the same pipeline into the FP16 2:4 GEMM of kernels/gemm/hgemm_sparse
+// (hgemm_sparse_tiled.cu:122-129: fp16 A_comp[M x K/2], fp16 B[K x N], fp32 C): in BYTES a stage
+// looks the same — 128 rows x 128 B of compressed values, BN x 256 B of the dense operand — but
+// covers 128 logical K instead of 256, carries half the metadata (16 B per row: one
+// tcgen05.cp.128x128b, one 32-bit column per MMA of K = 32, named as column pair + selector) and its four MMAs are
+// tcgen05.mma.sp.kind::f16 with fp32 accumulators, whose bits the EPI_I32 epilogue stores as they
+// are.  BN counts fp16 elements; the tensor maps are byte maps (inner extents doubled).  Only the
+// reference orientation is built: DENSE_MN, not TRANSPOSED, not PACKED.
+template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false, bool F16 = false>
 __global__ void __launch_bounds__(SparseCfg<BN>::THREADS, SparseCfg<BN>::CTAS_PER_SM)
 igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_d,
                     const SparseParams p) {
     using Cfg = SparseCfg<BN>;
     static_assert(!DENSE_MN || BN % 128 == 0, "MN-major dense operand is loaded in 128-column boxes");
+    static_assert(!F16 || (DENSE_MN && !TRANSPOSED && !PACKED && EPI == EPI_I32), "fp16: reference orientation only");
+    constexpr int kKRows = F16 ? 128 : kSpKLogical;          // logical K (= rows of B[K x N]) per stage
+    constexpr int kMetaStage = F16 ? 2048 : kSpMetaBytes;    // metadata bytes fetched per stage
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -210,7 +221,9 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                 const int n0 = seg.nrows < kBM - off0 ? seg.nrows : kBM - off0;   // rows from block rb
                 const int n1 = seg.nrows - n0;                                    // rows from block rb + 1
                 const int c0 = (seg.tile / p.tiles_r) * BN;
-                const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) * p.k_blocks *
+                // tiled metadata is laid out in 4 KiB blocks of 256 logical K; an fp16 k-block is half of one
+                const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) *
+                                                             (F16 ? (p.k_blocks + 1) / 2 : p.k_blocks) *
                                                              (PACKED ? kSpPackedBlock : kSpMetaBytes);
                 for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
@@ -232,11 +245,15 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                             if (n1 > 0) bulk_load(e_dst + j * 2048 + n0 * 16, blk1 + Cfg::A_BYTES + j * 2048, n1 * 16, bar);
                         }
                     } else {
-                        mbar_expect_tx(bar, Cfg::STAGE_BYTES);
+                        mbar_expect_tx(bar, Cfg::A_BYTES + Cfg::B_BYTES + kMetaStage);
                         tma_load_2d(a_smem0 + stage * Cfg::A_BYTES, &map_s, bar, kb * 128, r0);
                     }
                     const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
-                    if constexpr (DENSE_MN) {
+                    if constexpr (F16) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)    // [128 K rows x 64 fp16 columns] per box, byte map
+                            tma_load_2d(b_addr + j * (128 * kKRows), &map_d, bar, (c0 + j * 64) * 2, kb * kKRows);
+                    } else if constexpr (DENSE_MN) {
 #pragma unroll
                         for (int j = 0; j < BN / 128; ++j)   // [256 K rows x 128 C bytes] per box
                             tma_load_2d(b_addr + j * (128 * kSpKLogical), &map_d, bar, c0 + j * 128,
@@ -247,8 +264,8 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                             tma_load_2d(b_addr + j * (BN * 128), &map_d, bar, kb * kSpKLogical + j * 128, c0);
                     }
                     if constexpr (!PACKED)
-                        bulk_load(e_smem0 + stage * kSpMetaBytes, meta_row + static_cast<size_t>(kb) * kSpMetaBytes,
-                                  kSpMetaBytes, bar);
+                        bulk_load(e_smem0 + stage * kSpMetaBytes, meta_row + static_cast<size_t>(kb) * kMetaStage,
+                                  kMetaStage, bar);
                     issued |= 1u << stage;
                     issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -266,7 +283,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_i8(kBM, BN, DENSE_MN, true);
+            constexpr uint32_t idesc = F16 ? make_idesc_f16(kBM, BN, DENSE_MN, true) : make_idesc_i8(kBM, BN, DENSE_MN, true);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             WorkIter work(p, blockIdx.x, gridDim.x, num_tiles);
@@ -288,13 +305,22 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                     const uint32_t e_tmem = tmem_base + Cfg::E_BASE + stage * 8;
                     // metadata: rows are 16 B apart, 8-row groups 128 B apart, no swizzle
 #pragma unroll
-                    for (int j = 0; j < 2; ++j)
+                    for (int j = 0; j < (F16 ? 1 : 2); ++j)
                         tmem_cp_128x128b(e_tmem + 4 * j, make_smem_desc(e_addr + j * 2048, 0, 128, SWIZZLE_NONE_DESC));
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
                         const uint64_t a_desc = make_smem_desc(a_addr + ks * 32, 0, 1024, SWIZZLE_128B_DESC);
                         uint64_t b_desc;
-                        if constexpr (DENSE_MN) {
+                        if constexpr (F16) {
+                            // 32 K rows of 128 B per MMA; 64-column groups are one box (128 x 128 B) apart
+                            b_desc = make_smem_desc(b_addr + ks * (32 * 128), 128 * kKRows, 1024, SWIZZLE_128B_DESC);
+                            // metadata is addressed in pairs of 32-bit columns (what one kind::i8 MMA of
+                            // K = 64 consumes); a K = 32 fp16 MMA takes one column of the pair, chosen by
+                            // the selector in bits [0,2) of the instruction descriptor
+                            mma_f16_sp(d_tmem, a_desc, b_desc, e_tmem + (ks & ~1), idesc | static_cast<uint32_t>(ks & 1),
+                                       (kb != seg.kb0 || ks != 0) ? 1u : 0u);
+                            continue;
+                        } else if constexpr (DENSE_MN) {
                             b_desc = make_smem_desc(b_addr + ks * (64 * 128), 128 * kSpKLogical, 1024,
                                                     SWIZZLE_128B_DESC);
                         } else {

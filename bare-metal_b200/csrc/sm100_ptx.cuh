@@ -284,6 +284,26 @@ __device__ __forceinline__ void mma_i8_sp(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+// Instruction descriptor for kind::f16 with fp16 operands and fp32 accumulation: same fields as
+// kind::i8 with D format 1 = f32 and A / B format 0 = f16.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, bool b_mn_major, bool sparse) {
+    return (sparse ? (1u << 2) : 0u) | (1u << 4) | (b_mn_major ? (1u << 16) : 0u) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// 2:4-sparse fp16 MMA (K = 32 logical per instruction); metadata of the 128 rows in tensor memory
+__device__ __forceinline__ void mma_f16_sp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t e_tmem, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 }  // namespace bm
 
 // ----------------------------------------------------------------------------------------

@@ -20,7 +20,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import BM_B_KN, BM_B_NK, BM_META_REF, BM_META_ROWS, BM_META_TILED, BmError  # noqa: F401
+from ._lib import BM_B_KN, BM_B_NK, BM_META_REF, BM_META_REF_F16, BM_META_ROWS, BM_META_ROWS_F16, BM_META_TILED, BmError  # noqa: F401
 
 
 def _dev(t: torch.Tensor, dtype, name: str) -> int:
@@ -130,6 +130,31 @@ igemm_online_quant_inplace = igemm_online_quant_bankfree = igemm_warp_specialize
 def igemm_online_quant_bf_128x256(A, B, C, M, N, K, workspace=None):
     """igemm_online_quant_bf_128x256.cu:258-264: 256-column blocks of B share a factor."""
     return igemm_online_quant(A, B, C, M, N, K, 256, workspace)
+
+
+# --------------------------------------------------------------------------------------
+# FP16 2:4 GEMM: (A_compressed, B, C, metadata, M, N, K) — hgemm_sparse_tiled.cu:122-129
+# --------------------------------------------------------------------------------------
+def hgemm_sparse_tiled(A_comp, B, C, meta, M, N, K, meta_format=BM_META_REF_F16):
+    """C[M,N] fp32 = A_2:4[M,K] @ B[K,N]; A_comp fp16 [M,K/2], B fp16, metadata in the reference's
+    uint32 format (kernels/gemm/hgemm_sparse/sparse_meta.h), per-row bytes or the tiled order."""
+    L = _lib.load()
+    if meta.dtype == torch.uint8:
+        meta_ptr = _dev(meta, torch.uint8, "meta")
+    else:
+        meta_ptr = _dev(meta.view(torch.int32) if meta.dtype != torch.int32 else meta, torch.int32, "meta")
+    rc = L.bm_hgemm_sparse_f32(_dev(A_comp, torch.float16, "A_comp"), _dev(B, torch.float16, "B"),
+                               _out(C, torch.float32, "C"), meta_ptr, meta_format, M, N, K,
+                               C.stride(0) if C.dim() == 2 else N, _stream())
+    _lib.check(rc, "bm_hgemm_sparse_f32")
+    return C
+
+
+def hgemm_sparse_naive(A_comp, B, C, M, N, K):
+    """hgemm_sparse_naive.cu: the fixed pattern — kept positions {0,1} in every group (metadata 0x4444...)."""
+    count = (M // 16) * (K // 16) * 8
+    meta = torch.full((count,), 0x44444444, dtype=torch.int32, device=A_comp.device)
+    return hgemm_sparse_tiled(A_comp, B, C, meta, M, N, K)
 
 
 # --------------------------------------------------------------------------------------

@@ -124,12 +124,29 @@ int bm_pack_b_kn_to_nk(const int8_t *B_kn, int8_t *W_nk, int K, int N, void *str
                             one word (sparse_meta_int8.h:13-31,166-175)                      */
 #define BM_META_ROWS  1  /* bytes [R x K/8]: per row, byte j = groups 2j (low nibble), 2j+1  */
 #define BM_META_TILED 2  /* the kernel's own order, produced by bm_sp_pack_meta             */
+#define BM_META_REF_F16 3 /* FP16 sibling: uint32 words [(R/16)(K/16)8], 4 nibbles in bits 15:0
+                            (kernels/gemm/hgemm_sparse/sparse_meta.h:10-30); K % 16 == 0    */
+#define BM_META_ROWS_F16 4 /* BM_META_ROWS bytes, to be tiled for the FP16 kernel: tcgen05's
+                            kind::f16 keeps the metadata of rows i and i+8 interleaved across
+                            two lanes, so its tiled order differs from the int8 one; a tiled
+                            buffer made from format 3 or 4 serves bm_hgemm_sparse_f32 only     */
 
 /* bytes of a BM_META_TILED buffer for an R x K sparse operand */
 size_t bm_sp_meta_tiled_bytes(int R, int K);
 
 /* one-time metadata repack (device -> device) into the kernel's tiled order */
 int bm_sp_pack_meta(const void *meta_in, int meta_format, void *meta_tiled, int R, int K, void *stream);
+
+/* Replaces hgemm_sparse_tiled (kernels/gemm/hgemm_sparse/hgemm_sparse_tiled.cu:122-129) and, with
+ * all-0x44444444 metadata, hgemm_sparse_naive (hgemm_sparse_naive.cu; fixed positions {0,1}):
+ * FP16 2:4 GEMM, C[M x N] fp32 = A_sparse[M x K] * B[K x N], A stored as A_comp[M x K/2] fp16 (kept
+ * values, lower position first) + metadata, B fp16 row-major, fp32 accumulation on
+ * tcgen05.mma.sp.kind::f16.  `meta_format`: BM_META_REF_F16 (the reference's array, re-tiled into
+ * library scratch on every call), BM_META_ROWS / BM_META_ROWS_F16 (K % 32 == 0), or BM_META_TILED made
+ * by bm_sp_pack_meta from one of those two fp16 formats.  Operands are IEEE
+ * binary16 bits.  M % 16 == 0 for the reference format, K % 16 == 0, N % 16 == 0. */
+int bm_hgemm_sparse_f32(const uint16_t *A_comp, const uint16_t *B, float *C, const void *meta, int meta_format,
+                        int M, int N, int K, int64_t ldc, void *stream);
 
 /* Weight tooling: magnitude-prune a dense int8 matrix W[R x K] to 2:4 along K and compress it in one
  * pass.  Of every aligned group of 4 the two entries of largest |w| stay (ties: lower position),

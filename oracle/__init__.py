@@ -86,6 +86,11 @@ def lib():
         _sig(L.orc_meta_ref_to_rows, None, _p, _i, _i, _p)
         _sig(L.orc_prune_2_4_rows, None, _p, _i, _i, _p, _p)
         _sig(L.orc_online_quant_gemm, None, _p, _p, _p, _i, _i, _i, _i)
+        _sig(L.orc_h_sparse_meta_count, _sz, _i, _i)
+        _sig(L.orc_h_gen_sparse_2_4, None, _p, _i, _i, _u)
+        _sig(L.orc_h_compress_2_4, None, _p, _i, _i, _p, _p)
+        _sig(L.orc_h_cpu_sparse_gemm, None, _p, _p, _p, _i, _i, _i)
+        _sig(L.orc_h_decompress_2_4, None, _p, _p, _i, _i, _p)
         _sig(L.orc_gen_int8_uniform, None, _p, _sz, _u64, _u64)
         _sig(L.orc_gen_f32_uniform, None, _p, _sz, _f, _f, _u64, _u64)
         _sig(L.orc_gen_sparse_rows, None, _p, _p, _i, _i, _u64, _u64)
@@ -117,6 +122,31 @@ def ref():
         _sig(L.ref_cpu_sparse_gemm_int8, None, _p, _p, _p, _i, _i, _i)
         _ref = L
     return _ref
+
+
+_ref_f16 = None
+
+
+def ref_f16():
+    """The reference's FP16 2:4 host utilities (kernels/gemm/hgemm_sparse/sparse_meta.h), compiled in place."""
+    global _ref_f16
+    if _ref_f16 is None:
+        path = os.path.join(_HERE, "_ref", "libbm_ref_f16.so")
+        if not os.path.exists(path):
+            build(force=True)
+        if not os.path.exists(path):
+            raise FileNotFoundError("oracle/_ref/libbm_ref_f16.so has not been built")
+        L = C.CDLL(path)
+        _sig(L.ref_h_sparse_meta_count, _sz, _i, _i)
+        _sig(L.ref_h_gen_sparse_2_4, None, _p, _i, _i, _u)
+        _sig(L.ref_h_compress_2_4, None, _p, _i, _i, _p, _p)
+        _sig(L.ref_h_cpu_sparse_gemm, None, _p, _p, _p, _i, _i, _i)
+        _ref_f16 = L
+    return _ref_f16
+
+
+def have_ref_f16() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "libbm_ref_f16.so"))
 
 
 def _ptr(a: np.ndarray):
@@ -281,6 +311,48 @@ def online_quant_gemm(A_f16: np.ndarray, B_f16: np.ndarray, col_block: int = 128
     C = np.empty((M, N), np.float32)
     lib().orc_online_quant_gemm(_ptr(A), _ptr(B), _ptr(C), M, N, K, col_block)
     return C
+
+
+# --------------------------------------------------------------------------
+# FP16 2:4 utilities (kernels/gemm/hgemm_sparse/sparse_meta.h)
+# --------------------------------------------------------------------------
+def h_sparse_meta_count(M: int, K: int) -> int:
+    return int(lib().orc_h_sparse_meta_count(M, K))
+
+
+def h_gen_sparse_2_4(M: int, K: int, seed: int) -> np.ndarray:
+    out = np.empty((M, K), np.float32)
+    lib().orc_h_gen_sparse_2_4(_ptr(out), M, K, seed)
+    return out
+
+
+def h_compress_2_4(A_dense: np.ndarray):
+    """fp32 [M,K] with 2:4 zeros -> (A_comp fp16 [M,K/2], meta uint32 [(M/16)(K/16)8])."""
+    A = np.ascontiguousarray(A_dense, np.float32)
+    M, K = A.shape
+    comp = np.empty((M, K // 2), np.float16)
+    meta = np.empty(h_sparse_meta_count(M, K), np.uint32)
+    lib().orc_h_compress_2_4(_ptr(A), M, K, _ptr(comp), _ptr(meta))
+    return comp, meta
+
+
+def h_cpu_sparse_gemm(A_dense: np.ndarray, B: np.ndarray) -> np.ndarray:
+    A = np.ascontiguousarray(A_dense, np.float32)
+    B = np.ascontiguousarray(B, np.float32)
+    M, K = A.shape
+    N = B.shape[1]
+    out = np.empty((M, N), np.float32)
+    lib().orc_h_cpu_sparse_gemm(_ptr(A), _ptr(B), _ptr(out), M, N, K)
+    return out
+
+
+def h_decompress_2_4(comp: np.ndarray, meta: np.ndarray) -> np.ndarray:
+    comp = np.ascontiguousarray(comp, np.float16)
+    meta = np.ascontiguousarray(meta, np.uint32)
+    M, K2 = comp.shape
+    out = np.empty((M, 2 * K2), np.float16)
+    lib().orc_h_decompress_2_4(_ptr(comp), _ptr(meta), M, 2 * K2, _ptr(out))
+    return out
 
 
 def prune_2_4_rows(W: np.ndarray):

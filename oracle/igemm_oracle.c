@@ -572,6 +572,108 @@ ORC_API void orc_online_quant_gemm(const uint16_t *A, const uint16_t *B, float *
     free(max_a); free(max_b); free(Aq); free(Bq);
 }
 
+/* ------------------------------------------------------------------------
+ * kernels/gemm/hgemm_sparse/sparse_meta.h — FP16 sibling of the 2:4 utilities (K step 16).
+ * ---------------------------------------------------------------------- */
+/* :46-50 */
+ORC_API size_t orc_h_sparse_meta_count(int M, int K)
+{
+    return (size_t)(M / 16) * (size_t)(K / 16) * 8;
+}
+
+/* :65-105 — libc rand(); rows gid and gid+8 of a 16-row tile share positions; values in (-1,1) \ {0} */
+static float h_rval(void)
+{
+    float v;
+    do { v = ((float)rand() / RAND_MAX) * 2.0f - 1.0f; } while (v == 0.0f);
+    return v;
+}
+
+ORC_API void orc_h_gen_sparse_2_4(float *A_dense, int M, int K, unsigned int seed)
+{
+    srand(seed);
+    memset(A_dense, 0, (size_t)M * K * sizeof(float));
+    for (int mt = 0; mt < M / 16; mt++)
+        for (int gid = 0; gid < 8; gid++) {
+            int row_lo = mt * 16 + gid, row_hi = row_lo + 8;
+            for (int g = 0; g < K / 4; g++) {
+                int perm[4] = {0, 1, 2, 3};
+                for (int i = 3; i >= 2; i--) {
+                    int j = rand() % (i + 1);
+                    int t = perm[i]; perm[i] = perm[j]; perm[j] = t;
+                }
+                int p0 = perm[2], p1 = perm[3];
+                if (p0 > p1) { int t = p0; p0 = p1; p1 = t; }
+                A_dense[(size_t)row_lo * K + g * 4 + p0] = h_rval();
+                A_dense[(size_t)row_lo * K + g * 4 + p1] = h_rval();
+                A_dense[(size_t)row_hi * K + g * 4 + p0] = h_rval();
+                A_dense[(size_t)row_hi * K + g * 4 + p1] = h_rval();
+            }
+        }
+}
+
+/* :128-190 — positions by value != 0 (fall-backs 0 / 1), values rounded to fp16, one word per
+ * (16-row tile, K step of 16, gid) from the lower row, nibbles duplicated into bits 31:16 */
+ORC_API void orc_h_compress_2_4(const float *A_dense, int M, int K, uint16_t *A_comp, uint32_t *meta)
+{
+    int k_stored = K / 2, k_steps = K / 16;
+    memset(meta, 0, orc_h_sparse_meta_count(M, K) * sizeof(uint32_t));
+    for (int m = 0; m < M; m++) {
+        int m_tile = m / 16, tile_row = m % 16, gid = tile_row % 8;
+        for (int ks = 0; ks < K; ks += 16) {
+            uint32_t nibbles = 0;
+            for (int g = 0; g < 4; g++) {
+                const float *v = &A_dense[(size_t)m * K + ks + g * 4];
+                int idx0 = -1, idx1 = -1;
+                for (int i = 0; i < 4; i++)
+                    if (v[i] != 0.0f) {
+                        if (idx0 < 0) idx0 = i;
+                        else if (idx1 < 0) { idx1 = i; break; }
+                    }
+                if (idx0 < 0) idx0 = 0;
+                if (idx1 < 0) idx1 = 1;
+                A_comp[(size_t)m * k_stored + ks / 2 + g * 2 + 0] = f32_to_f16_rn(v[idx0]);
+                A_comp[(size_t)m * k_stored + ks / 2 + g * 2 + 1] = f32_to_f16_rn(v[idx1]);
+                nibbles |= (((uint32_t)idx1 << 2) | (uint32_t)idx0) << (g * 4);
+            }
+            if (tile_row < 8) meta[(m_tile * k_steps + ks / 16) * 8 + gid] = nibbles | (nibbles << 16);
+        }
+    }
+}
+
+/* :207-223 — fp32 reference, row x k x col, zeros skipped */
+ORC_API void orc_h_cpu_sparse_gemm(const float *A_dense, const float *B, float *C, int M, int N, int K)
+{
+    memset(C, 0, (size_t)M * N * sizeof(float));
+    for (int row = 0; row < M; row++)
+        for (int k = 0; k < K; k++) {
+            float a = A_dense[(size_t)row * K + k];
+            if (a == 0.0f) continue;
+            const float *b_row = &B[(size_t)k * N];
+            float *c_row = &C[(size_t)row * N];
+            for (int col = 0; col < N; col++) {
+                volatile float prod = a * b_row[col];      /* product and sum round separately (host code, -O2, no FMA) */
+                c_row[col] += prod;
+            }
+        }
+}
+
+/* inverse of the format: compressed fp16 + reference words -> dense fp16 bits (NEW, for tests) */
+ORC_API void orc_h_decompress_2_4(const uint16_t *A_comp, const uint32_t *meta, int M, int K, uint16_t *A_dense)
+{
+    int k_stored = K / 2, k_steps = K / 16;
+    memset(A_dense, 0, (size_t)M * K * sizeof(uint16_t));
+    for (int m = 0; m < M; m++)
+        for (int s = 0; s < k_steps; s++) {
+            uint32_t word = meta[((m / 16) * k_steps + s) * 8 + (m % 16) % 8];
+            for (int g = 0; g < 4; g++) {
+                uint32_t nib = (word >> (4 * g)) & 0xFu;
+                A_dense[(size_t)m * K + 16 * s + 4 * g + (nib & 3u)] = A_comp[(size_t)m * k_stored + 8 * s + 2 * g];
+                A_dense[(size_t)m * K + 16 * s + 4 * g + (nib >> 2)] = A_comp[(size_t)m * k_stored + 8 * s + 2 * g + 1];
+            }
+        }
+}
+
 /* [R x C] -> [C x R] byte transpose (layout helper for tests) */
 ORC_API void orc_transpose_i8(const int8_t *src, int8_t *dst, int R, int C)
 {

@@ -187,3 +187,26 @@ def test_online_quant_256_column_blocks_share_one_factor():
     c128, c256 = oracle.online_quant_gemm(A, B, 128), oracle.online_quant_gemm(A, B, 256)
     assert np.array_equal(c128[:, :128], c256[:, :128])            # the left block's maximum rules both
     assert not np.array_equal(c128[:, 128:], c256[:, 128:])
+
+
+@pytest.mark.skipif(not oracle.have_ref_f16(), reason="reference checkout absent and no prebuilt oracle/_ref")
+def test_fp16_sparse_utilities_equal_the_reference_headers():
+    """kernels/gemm/hgemm_sparse/sparse_meta.h compiled in place vs the restatement, bit for bit."""
+    R = oracle.ref_f16()
+    for M, K, N, seed in ((16, 16, 16, 1), (64, 96, 48, 999), (128, 256, 32, 7)):
+        assert oracle.h_sparse_meta_count(M, K) == R.ref_h_sparse_meta_count(M, K)
+        want = np.empty((M, K), np.float32)
+        R.ref_h_gen_sparse_2_4(want.ctypes.data, M, K, seed)
+        got = oracle.h_gen_sparse_2_4(M, K, seed)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        comp, meta = oracle.h_compress_2_4(got)
+        comp_w = np.empty((M, K // 2), np.float16)
+        meta_w = np.empty(oracle.h_sparse_meta_count(M, K), np.uint32)
+        R.ref_h_compress_2_4(want.ctypes.data, M, K, comp_w.ctypes.data, meta_w.ctypes.data)
+        assert np.array_equal(comp.view(np.uint16), comp_w.view(np.uint16)) and np.array_equal(meta, meta_w)
+        B = oracle.fill_random(K * N, 137).reshape(K, N)
+        c_w = np.empty((M, N), np.float32)
+        R.ref_h_cpu_sparse_gemm(want.ctypes.data, B.ctypes.data, c_w.ctypes.data, M, N, K)
+        assert np.array_equal(oracle.h_cpu_sparse_gemm(got, B).view(np.uint32), c_w.view(np.uint32))
+        # round trip through the format
+        assert np.array_equal(oracle.h_decompress_2_4(comp, meta).view(np.uint16), got.astype(np.float16).view(np.uint16))
