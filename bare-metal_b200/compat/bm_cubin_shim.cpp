@@ -20,7 +20,7 @@
 
 namespace {
 
-enum Kind { DENSE, DENSE_PERSISTENT, PER_CHANNEL, SPARSE, SPARSE_PERSISTENT, ONLINE_QUANT };
+enum Kind { DENSE, DENSE_PERSISTENT, PER_CHANNEL, SPARSE, SPARSE_PERSISTENT, ONLINE_QUANT, HSPARSE_TILED, HSPARSE_NAIVE };
 struct Served { const char* cubin; const char* symbol; Kind kind; };
 
 // cubin basename -> symbol -> argument layout (igemm.cu:52-59, igemm_persistent.cu:60-69,
@@ -43,6 +43,8 @@ const Served kServed[] = {
     {"igemm_online_quant_bankfree.sm_86.cubin", "igemm_online_quant_bankfree", ONLINE_QUANT},
     {"igemm_warp_specialized.sm_86.cubin", "igemm_warp_specialized", ONLINE_QUANT},
     {"igemm_sparse_tiled.sm_86.cubin", "igemm_sparse_tiled", SPARSE},
+    {"hgemm_sparse_tiled.sm_86.cubin", "hgemm_sparse_tiled", HSPARSE_TILED},                   // hgemm_sparse_tiled.cu:122-129
+    {"hgemm_sparse_naive.sm_86.cubin", "hgemm_sparse_naive", HSPARSE_NAIVE},                   // fixed positions {0,1}
     {"igemm_sparse_tiled_persistent.sm_86.cubin", "igemm_sparse_tiled_persistent", SPARSE_PERSISTENT},
 };
 
@@ -177,6 +179,38 @@ CUresult cuLaunchKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, uns
                                           reinterpret_cast<const uint16_t*>(arg<CUdeviceptr>(params, 1)),
                                           reinterpret_cast<float*>(arg<CUdeviceptr>(params, 2)), M, N, K, 128,
                                           reinterpret_cast<void*>(ws), ws_bytes, stream);
+            break;
+        }
+        case HSPARSE_TILED: {
+            const int M = arg<int>(params, 4), N = arg<int>(params, 5), K = arg<int>(params, 6);
+            rc = bm_hgemm_sparse_f32(reinterpret_cast<const uint16_t*>(arg<CUdeviceptr>(params, 0)),
+                                     reinterpret_cast<const uint16_t*>(arg<CUdeviceptr>(params, 1)),
+                                     reinterpret_cast<float*>(arg<CUdeviceptr>(params, 2)),
+                                     reinterpret_cast<const void*>(arg<CUdeviceptr>(params, 3)), BM_META_REF_F16, M, N, K, N,
+                                     stream);
+            break;
+        }
+        case HSPARSE_NAIVE: {
+            // the naive kernel has the pattern {0,1} built in: hand the library the matching metadata words
+            const int M = arg<int>(params, 3), N = arg<int>(params, 4), K = arg<int>(params, 5);
+            static CUdeviceptr words = 0;
+            static size_t n_words = 0;
+            const size_t need = static_cast<size_t>(M / 16) * (K / 16) * 8;
+            if (need > n_words) {
+                auto alloc = real<CUresult (*)(CUdeviceptr*, size_t)>("cuMemAlloc_v2");
+                auto release = real<CUresult (*)(CUdeviceptr)>("cuMemFree_v2");
+                auto sync = real<CUresult (*)()>("cuCtxSynchronize");
+                auto set32 = real<CUresult (*)(CUdeviceptr, unsigned, size_t)>("cuMemsetD32_v2");
+                if (!alloc || !release || !sync || !set32) return CUDA_ERROR_NOT_SUPPORTED;
+                if (words) { sync(); release(words); words = 0; n_words = 0; }
+                if (alloc(&words, need * 4) != CUDA_SUCCESS) return CUDA_ERROR_OUT_OF_MEMORY;
+                set32(words, 0x44444444u, need);
+                n_words = need;
+            }
+            rc = bm_hgemm_sparse_f32(reinterpret_cast<const uint16_t*>(arg<CUdeviceptr>(params, 0)),
+                                     reinterpret_cast<const uint16_t*>(arg<CUdeviceptr>(params, 1)),
+                                     reinterpret_cast<float*>(arg<CUdeviceptr>(params, 2)),
+                                     reinterpret_cast<const void*>(words), BM_META_REF_F16, M, N, K, N, stream);
             break;
         }
         case SPARSE:

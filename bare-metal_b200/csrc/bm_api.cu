@@ -687,7 +687,9 @@ int bm_hgemm_sparse_f32(const uint16_t* A_comp, const uint16_t* B, float* C, con
     if (int rc = current_device_state(&dev)) return rc;
     const int tiles_r = ceil_div(M, kBM);
     int bn = forced_bn();
-    if (bn != 128 && bn != 256) bn = (static_cast<long long>(tiles_r) * ceil_div(N, 256) >= dev->sm_count) ? 256 : 128;
+    // 128-column tiles: 4 stages and two accumulators fit; 256-column tiles leave room for 2 stages and
+    // one accumulator only and were measured slower (4096^3: 122 vs 99 us; 8192^3: 904 vs 801 us)
+    if (bn != 128 && bn != 256) bn = 128;
     CUtensorMap map_s, map_d;        // byte maps: compressed A is [M x K bytes], B is [K x 2N bytes]
     if (int rc = make_tensor_map_u8(&map_s, A_comp, K, M, K, 128, kBM, true)) return rc;
     if (int rc = make_tensor_map_u8(&map_d, B, 2 * static_cast<size_t>(N), K, 2 * static_cast<size_t>(N), 128, 128, true))

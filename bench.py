@@ -515,6 +515,16 @@ def side_measurements(ig, oracle, torch, devn, peaks):
     ms = timeit(lambda i: ig.igemm_online_quant(Ao[i % 3], Bo[i % 3], Co, Mo, No, Ko), 40)
     out["online_quant_fp16_4096"] = {"ms": ms, "tops": 2.0 * Mo * No * Ko / ms / 1e9}
     del Ao, Bo, Co
+    # FP16 2:4 sparse GEMM (kernels/gemm/hgemm_sparse), 4096^3, metadata tiled once
+    Mh = Nh = Kh = 4096
+    comp_h = [(torch.rand((Mh, Kh // 2), device=devn) * 2 - 1).half() for _ in range(3)]
+    B_h = [(torch.rand((Kh, Nh), device=devn) * 2 - 1).half() for _ in range(3)]
+    nib_h = torch.from_numpy(oracle.gen_sparse_rows(Mh, Kh, 0, sid("H", "A"))[1]).to(devn)
+    til_h = ig.sp_pack_meta(nib_h, ig.BM_META_ROWS_F16, Mh, Kh)
+    C_h = torch.empty((Mh, Nh), dtype=torch.float32, device=devn)
+    ms = timeit(lambda i: ig.hgemm_sparse_tiled(comp_h[i % 3], B_h[i % 3], C_h, til_h, Mh, Nh, Kh, ig.BM_META_TILED), 30)
+    out["hgemm_sparse_fp16_4096"] = {"ms": ms, "dense_equiv_tflops": 2.0 * Mh * Nh * Kh / ms / 1e9}
+    del comp_h, B_h, C_h
     # config 4: the four GEMMs of one 8192-token transformer layer, W8A8 -> fp16
     Mc = 8192
     chain = {}

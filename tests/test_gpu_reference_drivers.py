@@ -78,3 +78,26 @@ def test_reference_kernels_recompiled_for_sm100a_are_the_baseline_we_beat(tmp_pa
     their_oq = gate.parse_throughput(r.stdout.splitlines(), match="igemm_online_quant")
     our_oq = gate.parse_throughput(out, match="igemm_online_quant")
     assert our_oq["throughput"] > 10 * their_oq["throughput"], (their_oq, our_oq)
+
+
+def test_unmodified_fp16_sparse_bench_both_ways(tmp_path):
+    """kernels/gemm/hgemm_sparse/bench.cu, unmodified: with the reference's own kernels (compiled for
+    sm_100a) and served by this library through the shim.  Its three checks (fixed pattern naive + tiled,
+    arbitrary pattern tiled; 0.1 / 0.1) pass both ways; the library is faster on its timing line."""
+    exe = os.path.join(REF, "bench_hgemm_sparse")
+    cubins = os.path.join(REF, "cubins")
+    if not os.path.exists(exe) or not os.path.exists(os.path.join(cubins, "hgemm_sparse_tiled.sm_86.cubin")):
+        pytest.skip("reference fp16 sparse bench / kernels have not been built")
+    r = subprocess.run([exe, "1024", "1024", "1024"], capture_output=True, text=True, timeout=300, cwd=cubins)
+    assert r.returncode == 0, r.stderr[-2000:]
+    theirs = r.stdout.splitlines()
+    rc, ours, err = run_ref("bench_hgemm_sparse", [1024, 1024, 1024], tmp_path)
+    assert rc == 0, err[-2000:]
+    for out in (theirs, ours):
+        checks = [ln for ln in out if "PASS" in ln or "FAIL" in ln]
+        assert sum("PASS" in ln for ln in checks) >= 3 and not any("FAIL" in ln for ln in checks), checks
+
+    def tiled_ms(lines):
+        row = [ln.split() for ln in lines if ln.strip().startswith("tiled ")]
+        return float(row[-1][1])
+    assert tiled_ms(ours) < tiled_ms(theirs), (tiled_ms(ours), tiled_ms(theirs))
