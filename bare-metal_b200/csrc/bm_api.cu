@@ -321,8 +321,79 @@ static int launch_sparse_pair(const CUtensorMap& mw, const CUtensorMap& me, cons
         BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSpPairSmemBytes));
         configured[dev] = true;
     }
-    BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kSpPairSmemBytes, stream, 2, mw, me, mx, p));
+    BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kSpPairSmemBytes, stream, 2, mw, me, mx, mw, p));
+    return BM_OK;                                   // (no output tensor map in this orientation: mw fills the slot)
+}
+
+// the reference orientation (sparse operand on the left, B[K x C]) on CTA pairs: 256 rows x 224 columns
+template <int EPI, bool F16>
+static int launch_sparse_pair_left(const CUtensorMap& mw, const CUtensorMap& me, const CUtensorMap& mx,
+                                   const CUtensorMap& mo, const SparseParams& p, int pairs, cudaStream_t stream) {
+    auto kern = igemm_sparse_pair_kernel<EPI, true, F16>;
+    constexpr int smem = SpPairCfg<true>::SMEM_BYTES;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    BM_CUDA_TRY(cudaGetDevice(&dev));
+    if (!configured[dev]) {
+        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), smem, stream, 2, mw, me, mx, mo, p));
     return BM_OK;
+}
+
+// Sets up and launches the pair kernel in the reference orientation.  `elem` = bytes per operand element
+// (1: int8, 2: fp16); K counts logical elements, the tensor maps are byte maps.
+static int sparse_pair_left(int epi, bool f16, const void* S_comp, const uint8_t* meta_tiled, const void* B, void* out,
+                            int R, int Cn, int K, long long ld, float tensor_scale, DeviceState* dev,
+                            cudaStream_t stream) {
+    const int elem = f16 ? 2 : 1;
+    CUtensorMap map_w, map_e, map_x;
+    const size_t comp_bytes = static_cast<size_t>(K / 2) * elem;
+    if (int rc = make_tensor_map_u8(&map_w, S_comp, comp_bytes, R, comp_bytes, 128, kBM, true)) return rc;
+    const size_t units = meta_tiled_bytes(R, K) / 16;
+    if (int rc = make_tensor_map_u8(&map_e, meta_tiled, 16, units, 16, 16, f16 ? 128 : 256, false)) return rc;
+    const size_t row_bytes = static_cast<size_t>(Cn) * elem;
+    if (int rc = make_tensor_map_u8(&map_x, B, row_bytes, K, row_bytes, 128, f16 ? 128 : kSpKLogical, true)) return rc;
+    SparseParams p{};
+    p.epi.out = out;
+    p.epi.ld = ld;
+    p.epi.rows = R;
+    p.epi.cols = Cn;
+    p.epi.tensor_scale = tensor_scale;
+    p.epi.vec_ok = aligned16(out) && (static_cast<size_t>(ld) * 4) % 16 == 0;
+    CUtensorMap map_o = map_w;                       // placeholder unless the output qualifies for TMA stores
+    if (p.epi.vec_ok && !getenv("BM_NO_TMA_STORE")) {
+        if (int rc = make_tensor_map_out(&map_o, out, Cn, R, static_cast<size_t>(ld) * 4, 4)) return rc;
+        p.epi.tma_ok = 1;
+    }
+    p.meta_tiled = meta_tiled;
+    p.tiles_r = ceil_div(R, 256);
+    p.tiles_c = ceil_div(Cn, SpPairCfg<true>::BN);
+    p.k_blocks = ceil_div(K, f16 ? 128 : kSpKLogical);
+    p.status = dev->status;
+    p.sparse_rows = R;
+    const int pair_tiles = p.tiles_r * p.tiles_c;
+    const int max_pairs = dev->sm_count / 2;
+    const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+    if (f16) return launch_sparse_pair_left<EPI_I32, true>(map_w, map_e, map_x, map_o, p, pairs, stream);
+    if (epi == EPI_I32) return launch_sparse_pair_left<EPI_I32, false>(map_w, map_e, map_x, map_o, p, pairs, stream);
+    if (epi == EPI_F32_TENSOR) return launch_sparse_pair_left<EPI_F32_TENSOR, false>(map_w, map_e, map_x, map_o, p, pairs, stream);
+    return fail_msg(BM_ERR_LAYOUT, "unsupported epilogue for the sparse pair kernel");
+}
+
+// When the reference orientation runs on CTA pairs.  Measured against the lone-CTA kernel with 128-column
+// tiles: int8 is no faster on pairs (4096^3: 67.6 vs 58.4 us; 8192^3: 395 vs 371 us — with twice the MMA
+// rate of the dense kernel the operand reads from shared memory, ~100 B/clk, and the 60 B/clk of fills
+// meet the 128 B/clk of the shared memory, whatever the tile), so pairs are used for int8 only when the
+// tile width is forced to 224; fp16 gains 6-18 % once there are two waves of pair tiles
+// (4096^3: 90.7 vs 96.4 us; 8192 x 8192 x 4096: 315 vs 370 us).
+static bool sparse_pair_left_wanted(int R, int Cn, const DeviceState* dev, int forced, bool f16) {
+    if (forced == 224) return dev->sm_count >= 2;
+    if (forced != 0 || dev->sm_count < 2 || !f16) return false;
+    const char* e = getenv("BM_SPARSE_PAIR");
+    if (e && atoi(e) == 0) return false;
+    return static_cast<long long>(ceil_div(R, 256)) * ceil_div(Cn, SpPairCfg<true>::BN) >= dev->sm_count;
 }
 
 // BM_SPARSE_PAIR=0 keeps large sparse-weight problems on the single-CTA kernel (testing hook)
@@ -382,6 +453,10 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
         return fail_msg(BM_ERR_LAYOUT, "unsupported epilogue for the sparse pair kernel");
     }
     if (bn == 240) bn = 0;
+    if (mode == 0 && dense_mn && !packed && sparse_pair_left_wanted(R, Cn, dev, bn, false))
+        return sparse_pair_left(epi, false, S_comp, meta_tiled, Dn, out, R, Cn, K, ld, tensor_scale, dev,
+                                static_cast<cudaStream_t>(stream_v));
+    if (bn == 224) bn = 0;
 
     if (bn == 0) {
         if (mode == 1) {
@@ -690,6 +765,8 @@ int bm_hgemm_sparse_f32(const uint16_t* A_comp, const uint16_t* B, float* C, con
     if (int rc = current_device_state(&dev)) return rc;
     const int tiles_r = ceil_div(M, kBM);
     int bn = forced_bn();
+    if (sparse_pair_left_wanted(M, N, dev, bn, true))
+        return sparse_pair_left(EPI_I32, true, A_comp, tiled, B, C, M, N, K, ldc, 1.f, dev, static_cast<cudaStream_t>(stream_v));
     // 128-column tiles: 4 stages and two accumulators fit; 256-column tiles leave room for 2 stages and
     // one accumulator only and were measured slower (4096^3: 122 vs 99 us; 8192^3: 904 vs 801 us)
     if (bn != 128 && bn != 256) bn = 128;

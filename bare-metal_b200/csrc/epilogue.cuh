@@ -278,7 +278,7 @@ struct ParkedSource {
 // runs on across tiles).  With two strips a box is converted while the previous one is still being
 // read by its stores — what keeps the epilogue going when the stores go to other GPUs over NVLink.
 template <int EPI, int NC, int NBUF, class Source>
-__device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const OutMaps& maps, int n_maps, const Source& src,
+__device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const CUtensorMap* maps, int n_maps, const Source& src,
                                                int row0, int lane, int col0, const EpiStrip<NC>* strip, float lane_s,
                                                uint32_t stage_smem0, uint32_t& box_count, int col_limit) {
     using T = typename OutType<EPI>::type;
@@ -333,7 +333,7 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
             fence_proxy_async_smem();                        // generic-proxy writes -> visible to the TMA engine
             __syncwarp();
             if (lane == 0) {
-                for (int d = 0; d < n_maps; ++d) tma_store_2d(&maps.m[d], stage_smem, box_c0, row0);
+                for (int d = 0; d < n_maps; ++d) tma_store_2d(maps + d, stage_smem, box_c0, row0);
                 bulk_commit_group();
             }
             ++box_count;
@@ -342,7 +342,7 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const Ou
 }
 
 template <int EPI, int NC, int NBUF>
-__device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const OutMaps& maps, int n_maps,
+__device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const CUtensorMap* maps, int n_maps,
                                                       uint32_t taddr, int row0, int lane, int col0,
                                                       const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem0,
                                                       uint32_t& box_count, int col_limit) {

@@ -230,7 +230,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             bool stored = false;
             if constexpr (Cfg::NC * sizeof(typename OutType<EPI>::type) >= 128) {
                 if (p.epi.tma_ok) {
-                    drain_accumulator_tma<EPI, Cfg::NC, 1>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
+                    drain_accumulator_tma<EPI, Cfg::NC, 1>(p.epi, maps_out.m, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
                                                            lane_s, smem_base + Cfg::STORE_OFFSET + (warp - 2) * kStoreBoxBytes,
                                                            box_count, p.epi.cols);
                     stored = true;

@@ -294,7 +294,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kPairStoreBufs * kStoreBoxBytes;
             if (!TAIL_SPLIT || w.part < 0) {
                 if (p.epi.tma_ok)
-                    drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out, p.n_out, taddr, m0 + quarter * 32, lane,
+                    drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out.m, p.n_out, taddr, m0 + quarter * 32, lane,
                                                                         n0, strip, lane_s, my_stage, box_count, col_limit);
                 else
                     drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, col_limit, strip, lane_s);
@@ -326,7 +326,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     __threadfence();
                     auto ptr = [&](int part) -> const int32_t* { return part_of(part); };
                     if (p.epi.tma_ok)
-                        drain_tma_from<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out, p.n_out,
+                        drain_tma_from<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out.m, p.n_out,
                                                                      ParkedSource<decltype(ptr)>{ptr, p.tail_split, lane},
                                                                      m0 + quarter * 32, lane, n0, strip, lane_s, my_stage,
                                                                      box_count, p.epi.cols);

@@ -33,7 +33,8 @@ def run(comp, B16, meta, M, N, K, bn=None, fmt=None):
 
 
 @pytest.mark.parametrize("M,N,K,bn", [(128, 128, 128, 128), (256, 256, 256, 128), (16, 16, 16, None), (144, 272, 80, None),
-                                      (512, 512, 1040, 256), (384, 640, 2048, 256)])
+                                      (512, 512, 1040, 256), (384, 640, 2048, 256),
+                                      (256, 224, 128, 224), (400, 1008, 1040, 224), (144, 272, 80, 224)])   # 224: CTA pairs
 def test_arbitrary_patterns_bench_section_2(M, N, K, bn):
     """bench.cu:163-197 of hgemm_sparse: generator seed 999, compress_2_4_arbitrary, fp32 CPU reference on
     the unrounded data, tolerance 0.1 / 0.1 — plus the tight bound against the exact product of the

@@ -277,3 +277,25 @@ def test_prune_to_2_4_matches_the_oracle_and_feeds_the_sparse_gemm(R, K):
     assert_clean_status()
     pruned = oracle.decompress_rows(comp_want, nib_want)
     assert np.array_equal(C.cpu().numpy(), oracle.igemm(X, np.ascontiguousarray(pruned.T), threads=0))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 224, 256), (512, 448, 512), (144, 272, 1056), (400, 1008, 96), (1024, 2240, 2048)])
+def test_reference_orientation_on_cta_pairs(M, N, K):
+    """Sparse operand on the left, B[K x N], on CTA pairs (256 x 224 tiles; forced here, chosen by itself
+    for large shapes): exact int32 against the CPU GEMM of the decompressed matrix, ragged edges included,
+    and the fp32 reference ABI on top of the same integers."""
+    dense, comp, meta, B = bench_sparse_inputs(M, N, K)
+    want = oracle.igemm(dense, B, threads=0)
+    tiled = ig.sp_pack_meta(T(meta.view(np.int32)), ig.BM_META_REF, M, K)
+    buf = torch.full((M + 2, N), 0x5A5A5A5A, dtype=torch.int32, device=dev())
+    with forced_bn(224):
+        ig.igemm_sparse_i32(T(comp), tiled, ig.BM_META_TILED, T(B), buf[1:M + 1], M, N, K, ig.BM_B_KN)
+        assert_clean_status()
+        g = buf.cpu().numpy()
+        assert (g[0] == 0x5A5A5A5A).all() and (g[-1] == 0x5A5A5A5A).all(), "store outside the output"
+        assert np.array_equal(g[1:M + 1], want)
+        s = np.float32(1.0) / np.float32(127.0)
+        C = torch.full((M, N), -1.0, dtype=torch.float32, device=dev())
+        ig.igemm_sparse_tiled(T(comp), T(B), C, T(meta.view(np.int32)), M, N, K, float(s), float(s))
+        assert_clean_status()
+        assert np.array_equal(C.cpu().numpy().view(np.uint32), oracle.dequant_per_tensor(want, s, s).view(np.uint32))
