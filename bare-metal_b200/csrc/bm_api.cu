@@ -383,10 +383,8 @@ static int sparse_pair_left(int epi, bool f16, const void* S_comp, const uint8_t
 }
 
 // When the reference orientation runs on CTA pairs.  Measured against the lone-CTA kernel with 128-column
-// tiles: int8 is no faster on pairs (4096^3: 67.6 vs 58.4 us; 8192^3: 395 vs 371 us — with twice the MMA
-// rate of the dense kernel the operand reads from shared memory, ~100 B/clk, and the 60 B/clk of fills
-// meet the 128 B/clk of the shared memory, whatever the tile), so pairs are used for int8 only when the
-// tile width is forced to 224; fp16 gains 6-18 % once there are two waves of pair tiles
+// tiles: int8 is no faster on pairs (4096^3: 67.6 vs 58.4 us; 8192^3: 395 vs 371 us), so pairs are used
+// for int8 only when the tile width is forced to 224; fp16 gains 6-18 % once there are two waves of pair tiles
 // (4096^3: 90.7 vs 96.4 us; 8192 x 8192 x 4096: 315 vs 370 us).
 static bool sparse_pair_left_wanted(int R, int Cn, const DeviceState* dev, int forced, bool f16) {
     if (forced == 224) return dev->sm_count >= 2;
