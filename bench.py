@@ -161,7 +161,7 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the sparse / decode side measurements")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: fused = GEMM epilogue stores to all ranks over NVLink; nccl = GEMM then all-gather")
-    ap.add_argument("--workload", default="dense", choices=["dense", "sparse", "decode"],
+    ap.add_argument("--workload", default="dense", choices=["dense", "sparse", "decode", "online_quant", "hgemm_sparse"],
                     help="with --profile: which kernel to run (dense = the headline; sparse = config 3; "
                          "decode = config 5 at M=1)")
     ap.add_argument("--profile", action="store_true",
@@ -406,6 +406,24 @@ def profile_side_workload(args, ig, oracle, torch, devn):
         fn = lambda i: ig.w8a8_sparse_i32(X_d[i % sets], comp_d[i % sets], til_d[i % sets], C_d[i % sets], Ms, Ns, Ks)
         work = 2.0 * Ms * Ns * Ks
         unit = "dense-equiv TOPS"
+    elif args.workload == "online_quant":
+        Mo = No = Ko = 4096                  # 3 x (32 + 32) MiB of fp16 operands > L2
+        Ao = [torch.rand((Mo, Ko), device=devn, dtype=torch.float16) * 2 - 1 for _ in range(3)]
+        Bo = [torch.rand((Ko, No), device=devn, dtype=torch.float16) * 2 - 1 for _ in range(3)]
+        Co = torch.empty((Mo, No), dtype=torch.float32, device=devn)
+        fn = lambda i: ig.igemm_online_quant(Ao[i % 3], Bo[i % 3], Co, Mo, No, Ko)
+        work = 2.0 * Mo * No * Ko
+        unit = "TOPS"
+    elif args.workload == "hgemm_sparse":
+        Mh = Nh = Kh = 4096
+        comp_h = [(torch.rand((Mh, Kh // 2), device=devn) * 2 - 1).half() for _ in range(3)]
+        B_h = [(torch.rand((Kh, Nh), device=devn) * 2 - 1).half() for _ in range(3)]
+        nib_h = torch.from_numpy(oracle.gen_sparse_rows(Mh, Kh, 0, sid("H", "A"))[1]).to(devn)
+        til_h = ig.sp_pack_meta(nib_h, ig.BM_META_ROWS_F16, Mh, Kh)
+        C_h = torch.empty((Mh, Nh), dtype=torch.float32, device=devn)
+        fn = lambda i: ig.hgemm_sparse_tiled(comp_h[i % 3], B_h[i % 3], C_h, til_h, Mh, Nh, Kh, ig.BM_META_TILED)
+        work = 2.0 * Mh * Nh * Kh
+        unit = "dense-equiv TFLOPS"
     else:
         Nd, Kd, Md = 28672, 8192, 1
         comp, nib = oracle.gen_sparse_rows(Nd, Kd, 0, sid("C5", "W"))
@@ -429,7 +447,7 @@ def profile_side_workload(args, ig, oracle, torch, devn):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
-    value = work / ms / 1e9 if args.workload == "sparse" else work / ms / 1e6
+    value = work / ms / 1e6 if args.workload == "decode" else work / ms / 1e9
     print(json.dumps({"profile_run": True, "workload": args.workload, "value": value, "unit": unit, "ms_per_step": ms}),
           flush=True)
 
