@@ -78,6 +78,10 @@ struct SparseParams {
     // than 128 rows and only those rows are fetched (the packed blocks are row-contiguous).
     int row_balanced;
     int sparse_rows;                   // rows of the sparse operand (R)
+    // tile order of the pair kernel: 0 = row blocks of the sparse operand fastest (consecutive pairs share
+    // a tile of the dense operand), 1 = column tiles fastest (consecutive pairs share a block of the
+    // sparse operand — for weights larger than L2 and few column tiles, so each block leaves HBM once)
+    int col_first;
     int* sk_counters;                  // [tiles][epilogue warps], zero between launches (self-resetting)
     int32_t* sk_workspace;             // [CTAs][2: head / tail share][epilogue warps][NC x 32]
 };

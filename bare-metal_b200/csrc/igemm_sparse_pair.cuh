@@ -127,6 +127,8 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
     const int num_tiles = p.tiles_r * p.tiles_c;        // tiles of 256 channels x 240 tokens
+    auto tile_rb = [&](int tile) { return p.col_first ? tile / p.tiles_c : tile % p.tiles_r; };   // 256-row block
+    auto tile_cb = [&](int tile) { return p.col_first ? tile % p.tiles_c : tile / p.tiles_r; };   // column tile
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSpPairStages; ++s) {
@@ -163,8 +165,8 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                const int rb = (tile % p.tiles_r) * 2 + static_cast<int>(rank);       // 128-row block of the sparse operand
-                const int t0 = (tile / p.tiles_r) * kSpPairBN + static_cast<int>(rank) * kSpPairHalfN;
+                const int rb = tile_rb(tile) * 2 + static_cast<int>(rank);       // 128-row block of the sparse operand
+                const int t0 = tile_cb(tile) * kSpPairBN + static_cast<int>(rank) * kSpPairHalfN;
                 // metadata chunks of 128 rows x 16 B (= 128 logical K): 2 per int8 K block, 1 per fp16 K block;
                 // a row block holds 2 * ceil(K / 256) of them
                 const int chunks_per_rb = F16 ? ((p.k_blocks + 1) / 2) * 2 : p.k_blocks * 2;
@@ -259,8 +261,8 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         uint32_t acc = 0, acc_phase = 0;
         [[maybe_unused]] uint32_t box_count = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-            const int n0 = (tile % p.tiles_r) * 256 + static_cast<int>(rank) * 128;           // first sparse row (channel) of this CTA
-            const int tile_t0 = (tile / p.tiles_r) * kSpPairBN;
+            const int n0 = tile_rb(tile) * 256 + static_cast<int>(rank) * 128;           // first sparse row (channel) of this CTA
+            const int tile_t0 = tile_cb(tile) * kSpPairBN;
             const int t0 = tile_t0 + half * kSpPairNC;                                         // first accumulator column of this warp
             const int cross_extent = LEFT ? p.epi.cols : p.epi.rows;
             const int t_limit = cross_extent < tile_t0 + kSpPairBN ? cross_extent : tile_t0 + kSpPairBN;

@@ -299,3 +299,19 @@ def test_reference_orientation_on_cta_pairs(M, N, K):
         ig.igemm_sparse_tiled(T(comp), T(B), C, T(meta.view(np.int32)), M, N, K, float(s), float(s))
         assert_clean_status()
         assert np.array_equal(C.cpu().numpy().view(np.uint32), oracle.dequant_per_tensor(want, s, s).view(np.uint32))
+
+
+@pytest.mark.parametrize("order", [0, 1])
+def test_pair_kernel_tile_orders_give_the_same_integers(order):
+    """Sparse weights on CTA pairs with row blocks fastest and with column tiles fastest (the order picked
+    for weights larger than L2): exact int32 either way, ragged tiles on both axes."""
+    from _gpu import env
+    M, N, K = 500, 1100, 512                      # 3 token tiles of 240, 5 channel blocks of 256
+    comp, nib = oracle.gen_sparse_rows(N, K, 31, 1)
+    X = oracle.gen_int8((M, K), 31, 2)
+    tiled = ig.sp_pack_meta(T(nib), ig.BM_META_ROWS, N, K)
+    C = torch.full((M, N), -9, dtype=torch.int32, device=dev())
+    with env(BM_SPARSE_COL_FIRST=order), forced_bn(240):
+        ig.w8a8_sparse_i32(T(X), T(comp), tiled, C, M, N, K)
+    assert_clean_status()
+    assert np.array_equal(C.cpu().numpy(), oracle.igemm_nt(X, oracle.decompress_rows(comp, nib)))
