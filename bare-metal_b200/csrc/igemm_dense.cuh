@@ -63,9 +63,27 @@ struct DenseParams {
     // narrow tail (CTA-pair kernel, K-major B): the tiles of a partly filled last wave are computed as
     // two 256 x 128 halves by different pairs — no reduction, just smaller tiles for the idle pairs.
     int tail_narrow;
+    // tile order of the CTA-pair kernel: 0 = row tiles fastest over the whole matrix; G > 0 = bands of G
+    // row tiles, inside a band row tiles fastest (a wave then touches G row tiles x pairs/G column tiles)
+    int group_m;
     int* sk_counters;          // [tail tiles][2 CTAs][epilogue warps], zero between launches
     int32_t* sk_workspace;     // [tail tiles][tail_split][2 CTAs][epilogue warps][NC x 32]
 };
+
+// (row tile, column tile) of linear tile index `tile` under DenseParams::group_m
+__device__ __forceinline__ void pair_tile_coords(const DenseParams& p, int tile, int& tm, int& tn) {
+    if (p.group_m <= 0) {
+        tm = tile % p.tiles_m;
+        tn = tile / p.tiles_m;
+        return;
+    }
+    const int band_tiles = p.group_m * p.tiles_n;
+    const int band = tile / band_tiles, r = tile - band * band_tiles;
+    const int left = p.tiles_m - band * p.group_m;
+    const int rows = left < p.group_m ? left : p.group_m;       // the last band may be short
+    tm = band * p.group_m + r % rows;
+    tn = r / rows;
+}
 
 template <int BN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kDenseThreads, 1)

@@ -174,9 +174,11 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             PairWork w;
             while (ok && work.next(w)) {
                 const int tile = w.tile;
-                const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
+                int tm, tn;
+                pair_tile_coords(p, tile, tm, tn);
+                const int m0 = tm * 256 + static_cast<int>(rank) * kBM;
                 const bool narrow = w.nhalf >= 0;                       // 128-column half tile: 64 B rows per CTA
-                const int n0 = (tile / p.tiles_m) * kPairBN +
+                const int n0 = tn * kPairBN +
                                (narrow ? w.nhalf * 128 + static_cast<int>(rank) * 64 : static_cast<int>(rank) * kPairHalfN);
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
@@ -275,9 +277,11 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 #endif
         while (work.next(w)) {
             const int tile = w.tile;
-            const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(rank) * kBM;
+            int tm, tn;
+            pair_tile_coords(p, tile, tm, tn);
+            const int m0 = tm * 256 + static_cast<int>(rank) * kBM;
             const bool narrow = w.nhalf >= 0;                           // this warp drains 64 instead of 128 columns
-            const int n0 = (tile / p.tiles_m) * kPairBN + (narrow ? w.nhalf * 128 + half * 64 : half * kPairNC);
+            const int n0 = tn * kPairBN + (narrow ? w.nhalf * 128 + half * 64 : half * kPairNC);
             const int row = m0 + quarter * 32 + lane;
             // a narrow unit runs the same 128-column code with the column limit pulled in to 64
             const int col_limit = narrow ? (p.epi.cols < n0 + 64 ? p.epi.cols : n0 + 64) : p.epi.cols;

@@ -230,6 +230,20 @@ def test_narrow_tiles_in_the_last_wave(M, N, K):
 
 
 
+@pytest.mark.parametrize("group", [0, 3, 8])
+def test_banded_tile_order_gives_the_same_integers(group):
+    """Tile order of the pair kernel (plain, or bands of G row tiles — chosen for tall problems): the
+    integers do not depend on it; 21 row tiles make the last band short for G = 8."""
+    from _gpu import env
+    M, N, K = 5300, 1000, 256
+    A = oracle.gen_int8((M, K), 13, 1)
+    B = oracle.gen_int8((K, N), 13, 2)
+    with env(BM_DENSE_GROUP_M=group), forced_bn(256):
+        got = run_i32(A, B, ig.BM_B_NK, guard=True)
+    assert np.array_equal(got, oracle.igemm(A, B, threads=0))
+
+
+
 def test_bounded_wait_gives_up_with_a_status_and_the_context_survives():
     """Failure detection without a fault: a wait nobody satisfies runs out after 2 ms, the kernel
     returns, the status word names the wait, and the next GEMM on the same context is correct."""
