@@ -47,18 +47,13 @@ struct SpPairCfg {
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory over-subscribed");
 };
 
-constexpr int kSpPairBN = 240;                       // tokens per pair tile (MMA N): 2 x 240 + 32 = all 512 TMEM columns
-constexpr int kSpPairHalfN = kSpPairBN / 2;          // token rows staged per CTA
-constexpr int kSpPairABytes = 128 * 128;             // kept values
-constexpr int kSpPairBBytes = kSpPairHalfN * kSpKLogical;   // 30 KiB
-constexpr int kSpPairStageBytes = kSpPairABytes + kSpMetaBytes + kSpPairBBytes;   // 50 KiB
-constexpr int kSpPairStages = 4;
-constexpr int kSpPairEBase = 2 * kSpPairBN;          // metadata columns start after the accumulators
+// the sparse-weight orientation's figures under the names the launchers use
+constexpr int kSpPairBN = SpPairCfg<false>::BN;               // tokens per pair tile (MMA N): 2 x 240 + 32 = all 512 TMEM columns
+constexpr int kSpPairHalfN = SpPairCfg<false>::HALF_N;        // token rows staged per CTA
+constexpr int kSpPairABytes = SpPairCfg<false>::A_BYTES;      // kept values
 constexpr int kSpPairTmemCols = 512;
-constexpr int kSpPairNC = 128;                       // accumulator columns per epilogue warp (second half: 112 live)
-constexpr int kSpPairBarOffset = kSpPairStages * kSpPairStageBytes;
-constexpr int kSpPairStripOffset = kSpPairBarOffset + (2 * kSpPairStages + 5) * 8 + 16;
-constexpr int kSpPairSmemBytes = kSpPairStripOffset + kEpiWarps * (int)sizeof(EpiStrip<kSpPairNC>) + 1024;
+constexpr int kSpPairNC = SpPairCfg<false>::NC;               // accumulator columns per epilogue warp (second half: 112 / 96 live)
+constexpr int kSpPairSmemBytes = SpPairCfg<false>::SMEM_BYTES;
 
 __device__ __forceinline__ void tmem_cp_128x128b_pair(uint32_t taddr, uint64_t smem_desc) {
     asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
@@ -98,7 +93,7 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     constexpr int kSpPairStages = PC::STAGES;
     static_assert(!F16 || (LEFT && EPI == EPI_I32), "fp16: reference orientation, accumulator bits stored as they are");
     constexpr int kSpPairBN = PC::BN, kSpPairHalfN = PC::HALF_N, kSpPairBBytes = PC::B_BYTES;
-    constexpr int kSpPairStageBytes = PC::STAGE_BYTES, kSpPairEBase = PC::E_BASE, kSpPairBarOffset = PC::BAR_OFFSET;
+    constexpr int kSpPairEBase = PC::E_BASE, kSpPairBarOffset = PC::BAR_OFFSET;
     constexpr int kSpPairStripOffset = PC::STRIP_OFFSET;
     constexpr int kKRows = F16 ? 128 : kSpKLogical;          // logical K per stage
     constexpr int kMetaStage = F16 ? 2048 : kSpMetaBytes;
