@@ -164,6 +164,7 @@ def main() -> None:
     ap.add_argument("--workload", default="dense", choices=["dense", "sparse", "decode", "online_quant", "hgemm_sparse"],
                     help="with --profile: which kernel to run (dense = the headline; sparse = config 3; "
                          "decode = config 5 at M=1)")
+    ap.add_argument("--decode-m", type=int, default=1, help="with --profile --workload decode: number of tokens (1, 16, 64)")
     ap.add_argument("--profile", action="store_true",
                     help="profiler-friendly run: only warm-up + the timed steps of the headline kernel")
     args = ap.parse_args()
@@ -458,7 +459,7 @@ def profile_side_workload(args, ig, oracle, torch, devn):
         work = 2.0 * Mh * Nh * Kh
         unit = "dense-equiv TFLOPS"
     else:
-        Nd, Kd, Md = 28672, 8192, 1
+        Nd, Kd, Md = 28672, 8192, args.decode_m
         comp, nib = oracle.gen_sparse_rows(Nd, Kd, 0, sid("C5", "W"))
         comp_d = [torch.from_numpy(comp).to(devn) for _ in range(2)]
         til_d = [ig.sp_pack_meta(torch.from_numpy(nib).to(devn), ig.BM_META_ROWS, Nd, Kd) for _ in range(2)]
