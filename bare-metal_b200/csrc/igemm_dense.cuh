@@ -60,8 +60,8 @@ struct DenseParams {
     // partly filled wave takes 1/tail_split of a tile time.  Partial sums meet in sk_workspace and
     // the part that arrives last (per epilogue warp, counted in sk_counters) finishes the tile.
     int tail_first, tail_split;
-    // narrow tail (CTA-pair kernel, K-major B): the tiles of a partly filled last wave are computed as
-    // two 256 x 128 halves by different pairs — no reduction, just smaller tiles for the idle pairs.
+    // half-height tail (CTA-pair kernel): the tiles of a partly filled last wave are computed as two
+    // 128 x 256 halves by different pairs — no reduction, just shorter tiles for the idle pairs.
     int tail_narrow;
     // tile order of the CTA-pair kernel: 0 = row tiles fastest over the whole matrix; G > 0 = bands of G
     // row tiles, inside a band row tiles fastest (a wave then touches G row tiles x pairs/G column tiles)

@@ -46,7 +46,7 @@ constexpr int kPairSmemBytes = kPairStripOffset + kEpiWarps * (int)sizeof(EpiStr
 // split) one K range of one tail tile.
 struct PairWork {
     int tile, kb0, kb1, part;           // part < 0: the whole K range
-    int nhalf;                          // < 0: all 256 columns; 0 / 1: columns [128 nhalf, +128) only
+    int nhalf;                          // < 0: all 256 rows; 0 / 1: rows [128 nhalf, +128) of the tile only (a half-height unit)
 };
 struct PairWorkIter {
     int next_tile, pairs, tiles, tail_first, split, k_blocks, pair;
@@ -109,7 +109,7 @@ __device__ unsigned long long g_pair_trace[74][kTraceTiles][kTraceSlots];
 template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const __grid_constant__ CUtensorMap map_b_narrow, const __grid_constant__ OutMaps maps_out,
+                        const __grid_constant__ CUtensorMap map_a_short, const __grid_constant__ OutMaps maps_out,
                         const DenseParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -170,27 +170,28 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
-                              !B_MN && p.tail_narrow != 0);
+                              p.tail_narrow != 0);
             PairWork w;
             while (ok && work.next(w)) {
                 const int tile = w.tile;
                 int tm, tn;
                 pair_tile_coords(p, tile, tm, tn);
                 const int m0 = tm * 256 + static_cast<int>(rank) * kBM;
-                const bool narrow = w.nhalf >= 0;                       // 128-column half tile: 64 B rows per CTA
-                const int n0 = tn * kPairBN +
-                               (narrow ? w.nhalf * 128 + static_cast<int>(rank) * 64 : static_cast<int>(rank) * kPairHalfN);
+                // half-height unit: 128 rows of the tile, 64 per CTA (an M = 128 pair MMA); B as for a whole tile
+                const bool narrow = w.nhalf >= 0;
+                const int n0 = tn * kPairBN + static_cast<int>(rank) * kPairHalfN;
+                const int m0s = tm * 256 + w.nhalf * 128 + static_cast<int>(rank) * 64;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
                     const uint32_t leader_full = mapa_shared(full_bar(stage), 0);
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), narrow ? 2 * (kABytes + 64 * kBK) : 2 * kPairStageBytes);
-                    tma_load_2d_pair(a_smem0 + stage * kABytes, &map_a, leader_full, kb * kBK, m0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), narrow ? 2 * (kABytes / 2 + kPairBBytes) : 2 * kPairStageBytes);
+                    if (narrow) tma_load_2d_pair(a_smem0 + stage * kABytes, &map_a_short, leader_full, kb * kBK, m0s);
+                    else        tma_load_2d_pair(a_smem0 + stage * kABytes, &map_a, leader_full, kb * kBK, m0);
                     if constexpr (B_MN)
                         tma_load_2d_pair(b_smem0 + stage * kPairBBytes, &map_b, leader_full, n0, kb * kBK);
                     else
-                        tma_load_2d_pair(b_smem0 + stage * kPairBBytes, narrow ? &map_b_narrow : &map_b, leader_full,
-                                         kb * kBK, n0);
+                        tma_load_2d_pair(b_smem0 + stage * kPairBBytes, &map_b, leader_full, kb * kBK, n0);
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -199,11 +200,11 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // ------------------------------------------------------------------ MMA issuer (leader only)
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc_full = make_idesc_i8(256, kPairBN, B_MN, false);
-            constexpr uint32_t idesc_narrow = make_idesc_i8(256, 128, B_MN, false);
+            constexpr uint32_t idesc_narrow = make_idesc_i8(128, kPairBN, B_MN, false);   // 64 rows per CTA
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
-                              !B_MN && p.tail_narrow != 0);
+                              p.tail_narrow != 0);
             PairWork w;
 #ifdef BM_TILE_TRACE
             int trace_t = 0;
@@ -270,7 +271,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         EpiStrip<kPairNC>* strip = reinterpret_cast<EpiStrip<kPairNC>*>(smem_gen + kPairStripOffset) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0, box_count = 0;
         PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
-                              !B_MN && p.tail_narrow != 0);
+                              p.tail_narrow != 0);
         PairWork w;
 #ifdef BM_TILE_TRACE
         int trace_e = 0;
@@ -280,10 +281,15 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             int tm, tn;
             pair_tile_coords(p, tile, tm, tn);
             const int m0 = tm * 256 + static_cast<int>(rank) * kBM;
-            const bool narrow = w.nhalf >= 0;                           // this warp drains 64 instead of 128 columns
-            const int n0 = tn * kPairBN + (narrow ? w.nhalf * 128 + half * 64 : half * kPairNC);
-            const int row = m0 + quarter * 32 + lane;
-            // a narrow unit runs the same 128-column code with the column limit pulled in to 64
+            // Whole tile: lanes = the CTA's 128 rows, this warp drains TMEM columns [128 half, +128).
+            // Half-height unit (M = 128 on the pair): the CTA's 64 rows sit in lanes 0-63 for output columns
+            // [0,128) and again in lanes 64-127 for output columns [128,256); 128 TMEM columns are in use and
+            // this warp drains 64 of them.
+            const bool narrow = w.nhalf >= 0;
+            const int row_base = narrow ? tm * 256 + w.nhalf * 128 + static_cast<int>(rank) * 64 + (quarter & 1) * 32
+                                        : m0 + quarter * 32;
+            const int n0 = tn * kPairBN + (narrow ? (quarter >> 1) * 128 + half * 64 : half * kPairNC);
+            const int row = row_base + lane;
             const int col_limit = narrow ? (p.epi.cols < n0 + 64 ? p.epi.cols : n0 + 64) : p.epi.cols;
             stage_strip<EPI, kPairNC, false>(p.epi, strip, n0, lane);
             const float lane_s = lane_scale_of<EPI, false>(p.epi, row);
@@ -298,7 +304,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kPairStoreBufs * kStoreBoxBytes;
             if (!TAIL_SPLIT || w.part < 0) {
                 if (p.epi.tma_ok)
-                    drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out.m, p.n_out, taddr, m0 + quarter * 32, lane,
+                    drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out.m, p.n_out, taddr, row_base, lane,
                                                                         n0, strip, lane_s, my_stage, box_count, col_limit);
                 else
                     drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, col_limit, strip, lane_s);

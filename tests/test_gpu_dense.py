@@ -205,15 +205,18 @@ def test_tail_split_of_the_last_wave(M, N, K, layout):
 
 
 @pytest.mark.parametrize("M,N,K", [(2560, 2304, 512), (2500, 2256, 272), (2500, 2250, 144), (2816, 2048, 1024)])
-def test_narrow_tiles_in_the_last_wave(M, N, K):
-    """K-major weights, more 256x256 tiles than CTA pairs and a last wave at most half full: its tiles
-    are computed as two 256x128 halves by different pairs.  Same integers as with the narrow tail
-    off, for every epilogue, ragged edges included; canary rows catch stores outside the output."""
+def test_half_height_tiles_in_the_last_wave(M, N, K):
+    """More 256x256 tiles than CTA pairs and a last wave at most half full: its tiles are computed as two
+    128x256 halves by different pairs (M = 128 pair MMAs, 64 rows per CTA).  Same integers as with the
+    half-height tail off, for every epilogue and both weight layouts, ragged edges included; canary rows
+    catch stores outside the output."""
     from _gpu import env
     A = oracle.gen_int8((M, K), 12, 1)
     B = oracle.gen_int8((K, N), 12, 2)
     acc = oracle.igemm(A, B, threads=0)
     assert np.array_equal(run_i32(A, B, ig.BM_B_NK, guard=True), acc)
+    if N % 16 == 0:
+        assert np.array_equal(run_i32(A, B, ig.BM_B_KN, guard=True), acc)
     with env(BM_TAIL_NARROW=0):
         assert np.array_equal(run_i32(A, B, ig.BM_B_NK, guard=True), acc)
     Bd = T(B.T)
