@@ -22,7 +22,8 @@ SIGNATURES = {
     "bm_igemm_i8_f32": (_i, [_p, _p, _p, _i, _i, _i, _f, _f, _i64, _i, _p]),
     "bm_igemm_i8_f32_perchannel": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _i64, _i, _p]),
     "bm_w8a8_f16": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i64, _i, _p]),
-    "bm_w8a8_f16_gather": (_i, [_p, _p, _p, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
+    "bm_w8a8_f16_gather": (_i, [_p, _p, _p, _i, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
+    "bm_gather_slab_f16": (_i, [_p, _i, _i, _i, _i, _i64, _p]),
     "bm_quantize_rows_f16": (_i, [_p, _p, _p, _i, _i, _p]),
     "bm_pack_b_kn_to_nk": (_i, [_p, _p, _i, _i, _p]),
     "bm_prune_2_4_i8": (_i, [_p, _p, _p, _i, _i, _p]),
@@ -40,7 +41,12 @@ SIGNATURES = {
     "bm_sp_pack_weights": (_i, [_p, _p, _i, _p, _i, _i, _p]),
     "bm_w8a8_sparse_i32_packed": (_i, [_p, _p, _p, _i, _i, _i, _i64, _p]),
     "bm_w8a8_sparse_f16_packed": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i64, _p]),
+    "bm_noalloc_last_device_status": (_i, [C.POINTER(_i)]),
+    "bm_noalloc_selftest_bounded_wait": (_i, [C.c_uint, C.POINTER(_i)]),
     "bm_last_device_status": (_i, [C.POINTER(_i)]),
+    "bm_set_option": (_i, [C.c_char_p, _i]),
+    "bm_get_option": (_i, [C.c_char_p, C.POINTER(_i)]),
+    "bm_tensor_map_cache_stats": (_i, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "bm_selftest_bounded_wait": (_i, [C.c_uint, C.POINTER(_i)]),
     "bm_last_error_string": (C.c_char_p, []),
     "bm_shutdown": (None, []),
@@ -70,6 +76,16 @@ def load():
             fn.argtypes = args
         _lib = lib
     return _lib
+
+
+def set_option(name: str, value: int) -> None:
+    check(load().bm_set_option(name.encode(), int(value)), f"bm_set_option({name})")
+
+
+def get_option(name: str) -> int:
+    v = _i(0)
+    check(load().bm_get_option(name.encode(), C.byref(v)), f"bm_get_option({name})")
+    return v.value
 
 
 def check(rc: int, what: str) -> None:

@@ -11,17 +11,15 @@
 #include "pack_kernels.cuh"
 #include "online_quant_kernels.cuh"
 #include "quantize_kernels.cuh"
+#include "gather_kernels.cuh"
 
 namespace bm {
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-// Testing hook: BM_FORCE_BN=<width> pins the tile width so every instantiation can be
-// exercised on small problems.  Unset (the default) lets the launcher choose.
-static int forced_bn() {
-    const char* e = getenv("BM_FORCE_BN");
-    return e ? atoi(e) : 0;
-}
+// Testing hook: option "force_bn" pins the tile width so every instantiation can be exercised
+// on small problems.  0 (the default) lets the launcher choose.
+static int forced_bn() { return opt(OPT_FORCE_BN); }
 
 static int validate_epilogue(int epi, const void* out, long long ld, int cols, const float* row_scale,
                              const float* col_scale, const int* col_zero) {
@@ -42,41 +40,25 @@ static int launch_dense_inst(const CUtensorMap& ma, const CUtensorMap& mb, const
                              const DenseParams& p, int grid, cudaStream_t stream) {
     using Cfg = DenseCfg<BN>;
     auto kern = igemm_dense_kernel<BN, B_MN, EPI>;
-    static bool configured[kMaxDevices] = {};
-    int dev = 0;
-    BM_CUDA_TRY(cudaGetDevice(&dev));
-    if (!configured[dev]) {
-        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        configured[dev] = true;
-    }
+    static ConfiguredFlags flags;
+    if (int rc = ensure_smem_limit(flags, kern, Cfg::SMEM_BYTES)) return rc;
     BM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(kDenseThreads), Cfg::SMEM_BYTES, stream, 1, ma, mb, mo, p));
     return BM_OK;
 }
 
 // CTA-pair kernel: 2-CTA clusters, one pair per two SMs, 256 x 256 tiles
-template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
+template <bool B_MN, int EPI>
 static int launch_dense_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mbn, const OutMaps& mo,
                              const DenseParams& p, int pairs, cudaStream_t stream) {
-    if constexpr (!TAIL_SPLIT) {
-        if (p.tail_split > 1) return launch_dense_pair<B_MN, EPI, true>(ma, mb, mbn, mo, p, pairs, stream);
-    }
-    auto kern = igemm_dense_pair_kernel<B_MN, EPI, TAIL_SPLIT>;
-    static bool configured[kMaxDevices] = {};
-    int dev = 0;
-    BM_CUDA_TRY(cudaGetDevice(&dev));
-    if (!configured[dev]) {
-        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
-        configured[dev] = true;
-    }
+    auto kern = igemm_dense_pair_kernel<B_MN, EPI>;
+    static ConfiguredFlags flags;
+    if (int rc = ensure_smem_limit(flags, kern, kPairSmemBytes)) return rc;
     BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kPairSmemBytes, stream, 2, ma, mb, mbn, mo, p));
     return BM_OK;
 }
 
-// BM_DENSE_PAIR=0 keeps large problems on the single-CTA kernel (testing hook; default on)
-static bool pair_enabled() {
-    const char* e = getenv("BM_DENSE_PAIR");
-    return !e || atoi(e) != 0;
-}
+// option "dense_pair" = 0 keeps large problems on the single-CTA kernel (testing hook; default on)
+static bool pair_enabled() { return opt(OPT_DENSE_PAIR) != 0; }
 
 template <bool B_MN, int EPI>
 static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& mo,
@@ -92,7 +74,8 @@ static int launch_dense_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb,
 
 static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M, int N, int K, long long ldc,
                       int b_layout, float tensor_scale, const float* row_scale, const float* col_scale,
-                      const int* col_zero, void* stream_v, void* const* peers = nullptr, int n_peers = 0) {
+                      const int* col_zero, void* stream_v, void* const* peers = nullptr, int n_peers = 0,
+                      int self_index = -1) {
     if (!A || !B) return fail_msg(BM_ERR_NULL, "operand pointer is NULL");
     if (M <= 0 || N <= 0 || K <= 0) return fail_msg(BM_ERR_SHAPE, "M, N, K must be positive");
     if (b_layout != BM_B_KN && b_layout != BM_B_NK) return fail_msg(BM_ERR_LAYOUT, "unknown B layout tag");
@@ -168,7 +151,15 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
         p.n_out = n_peers;
         p.epi.tma_ok = 1;
         p.epi.vec_ok = 1;
-    } else if (p.epi.vec_ok && !getenv("BM_NO_TMA_STORE")) {
+        // every destination but the GPU's own buffer is reached over NVLink: those stores are paced
+        const bool self_ok = self_index >= 0 && self_index < n_peers;
+        p.pace.first = self_ok ? self_index : 0;
+        p.pace.remote_mask = ((1u << n_peers) - 1u) & ~(self_ok ? 1u << self_index : 0u);
+        p.pace.clock = dev->link_clock;
+        const int gbs = opt(OPT_GATHER_GBS);
+        // one remote store = one 32-row x 128-byte box = 4 KiB; virtual-clock units are 1/16 ns
+        p.pace.cost = gbs > 0 ? static_cast<unsigned>((4096.0 * 16.0) / gbs + 0.5) : 0u;
+    } else if (p.epi.vec_ok && opt(OPT_TMA_STORE) != 0) {
         if (int rc = make_tensor_map_out(&map_out.m[0], C, N, M, static_cast<size_t>(ldc) * out_elem_size(epi),
                                          static_cast<int>(out_elem_size(epi))))
             return rc;
@@ -193,39 +184,20 @@ static int dense_gemm(int epi, const int8_t* A, const int8_t* B, void* C, int M,
         // tiles to reuse.  Measured (medians, interleaved): 16384 x 4096 x 4096 +4.4 %, 8192 x 4096 x 11008
         // +5.7 %, 8192 x 4096 x 4096 +1.6 %; wide problems (8192 x 22016 x 4096: -1.8 %) keep the plain order.
         p.group_m = (p.tiles_m >= 2 * p.tiles_n && p.tiles_m >= 16) ? 8 : 0;
-        if (const char* e = getenv("BM_DENSE_GROUP_M")) p.group_m = atoi(e);
-        // Tail split (BM_TAIL_SPLIT=S, S in 2..4): cut each tile of a partly filled last wave into S
-        // K ranges for different pairs.  Off by default: at 4096^3 (34 tail tiles on 74 pairs, S = 2)
-        // it was measured 15 % SLOWER (69.5 vs 60.3 us on the same box) — parking 128 KiB per CTA,
-        // the fence/atomic hand-off and re-reading both parts cost more than the half tile they save.
+        if (opt(OPT_DENSE_GROUP_M) >= 0) p.group_m = opt(OPT_DENSE_GROUP_M);
+        // Half-height tail: when at most half of the pairs would work in the last wave, its tiles are
+        // computed as two 128 x 256 halves by different pairs (M = 128 pair MMAs, 64 rows per CTA; no
+        // reduction).  Worth only ~1 % (4096^3: 48.1 -> 47.8 us): a K = 32 MMA step chained on one
+        // accumulator takes ~128 clocks whether it is 256 x 256, 256 x 128 or 128 x 256, so a smaller unit
+        // saves operand waits, not MMA time.  Option "tail_narrow" = 0 switches it off.  (Cutting the tail
+        // tiles along K instead — partial sums parked in global memory, last arrival finishes — was
+        // measured 15 % SLOWER at 4096^3, 69.5 vs 60.3 us, and is not built.)
         {
             const int rem = pair_tiles % pairs;
-            int split = 1;
-            if (const char* e = getenv("BM_TAIL_SPLIT")) {
-                const int f = atoi(e);
-                if (f > 1 && f <= 4 && rem > 0 && pair_tiles > pairs && f * rem <= pairs && f <= p.k_blocks) split = f;
-            }
-            // Half-height tail (default): when at most half of the pairs would work in the last wave, its
-            // tiles are computed as two 128 x 256 halves by different pairs (M = 128 pair MMAs, 64 rows per
-            // CTA; no reduction).  Worth only ~1 % (4096^3: 48.1 -> 47.8 us): a K = 32 MMA step chained on one
-            // accumulator takes ~128 clocks whether it is 256 x 256, 256 x 128 or 128 x 256, so a smaller
-            // unit saves operand waits, not MMA time.  BM_TAIL_NARROW=0 switches it off.
-            if (split == 1 && rem > 0 && pair_tiles > pairs && 2 * rem <= pairs) {
-                const char* e = getenv("BM_TAIL_NARROW");
-                if (!e || atoi(e) != 0) {
-                    if (int rc = make_tensor_map_u8(&map_a_short, A, K, M, K, kBK, 64, true)) return rc;
-                    p.tail_first = pair_tiles - rem;
-                    p.tail_narrow = 1;
-                }
-            }
-            if (split > 1) {
-                const size_t slice_ints = static_cast<size_t>(kPairNC) * 32;
-                const size_t ws_bytes = static_cast<size_t>(rem) * split * 2 * kEpiWarps * slice_ints * sizeof(int32_t);
-                if (int rc = ensure_split_k(dev, ws_bytes, static_cast<size_t>(rem) * 2 * kEpiWarps)) return rc;
+            if (rem > 0 && pair_tiles > pairs && 2 * rem <= pairs && opt(OPT_TAIL_NARROW) != 0) {
+                if (int rc = make_tensor_map_u8(&map_a_short, A, K, M, K, kBK, 64, true)) return rc;
                 p.tail_first = pair_tiles - rem;
-                p.tail_split = split;
-                p.sk_workspace = static_cast<int32_t*>(dev->sk_workspace);
-                p.sk_counters = dev->sk_counters;
+                p.tail_narrow = 1;
             }
         }
 #define BM_PAIR_CASE(E)                                                                         \
@@ -306,13 +278,8 @@ static int launch_sparse_inst(const CUtensorMap& ms, const CUtensorMap& md, cons
                               cudaStream_t stream) {
     using Cfg = SparseCfg<BN>;
     auto kern = igemm_sparse_kernel<BN, DENSE_MN, TRANSPOSED, EPI, PACKED>;
-    static bool configured[kMaxDevices] = {};
-    int dev = 0;
-    BM_CUDA_TRY(cudaGetDevice(&dev));
-    if (!configured[dev]) {
-        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        configured[dev] = true;
-    }
+    static ConfiguredFlags flags;
+    if (int rc = ensure_smem_limit(flags, kern, Cfg::SMEM_BYTES)) return rc;
     BM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, 1, ms, md, p));
     return BM_OK;
 }
@@ -322,13 +289,8 @@ template <int EPI>
 static int launch_sparse_pair(const CUtensorMap& mw, const CUtensorMap& me, const CUtensorMap& mx, const SparseParams& p,
                               int pairs, cudaStream_t stream) {
     auto kern = igemm_sparse_pair_kernel<EPI>;
-    static bool configured[kMaxDevices] = {};
-    int dev = 0;
-    BM_CUDA_TRY(cudaGetDevice(&dev));
-    if (!configured[dev]) {
-        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSpPairSmemBytes));
-        configured[dev] = true;
-    }
+    static ConfiguredFlags flags;
+    if (int rc = ensure_smem_limit(flags, kern, kSpPairSmemBytes)) return rc;
     BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), kSpPairSmemBytes, stream, 2, mw, me, mx, mw, p));
     return BM_OK;                                   // (no output tensor map in this orientation: mw fills the slot)
 }
@@ -339,13 +301,8 @@ static int launch_sparse_pair_left(const CUtensorMap& mw, const CUtensorMap& me,
                                    const CUtensorMap& mo, const SparseParams& p, int pairs, cudaStream_t stream) {
     auto kern = igemm_sparse_pair_kernel<EPI, true, F16>;
     constexpr int smem = SpPairCfg<true>::SMEM_BYTES;
-    static bool configured[kMaxDevices] = {};
-    int dev = 0;
-    BM_CUDA_TRY(cudaGetDevice(&dev));
-    if (!configured[dev]) {
-        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        configured[dev] = true;
-    }
+    static ConfiguredFlags flags;
+    if (int rc = ensure_smem_limit(flags, kern, smem)) return rc;
     BM_CUDA_TRY(launch_pdl(kern, dim3(2 * pairs), dim3(kDenseThreads), smem, stream, 2, mw, me, mx, mo, p));
     return BM_OK;
 }
@@ -371,7 +328,7 @@ static int sparse_pair_left(int epi, bool f16, const void* S_comp, const uint8_t
     p.epi.tensor_scale = tensor_scale;
     p.epi.vec_ok = aligned16(out) && (static_cast<size_t>(ld) * 4) % 16 == 0;
     CUtensorMap map_o = map_w;                       // placeholder unless the output qualifies for TMA stores
-    if (p.epi.vec_ok && !getenv("BM_NO_TMA_STORE")) {
+    if (p.epi.vec_ok && opt(OPT_TMA_STORE) != 0) {
         if (int rc = make_tensor_map_out(&map_o, out, Cn, R, static_cast<size_t>(ld) * 4, 4)) return rc;
         p.epi.tma_ok = 1;
     }
@@ -397,16 +354,12 @@ static int sparse_pair_left(int epi, bool f16, const void* S_comp, const uint8_t
 static bool sparse_pair_left_wanted(int R, int Cn, const DeviceState* dev, int forced, bool f16) {
     if (forced == 224) return dev->sm_count >= 2;
     if (forced != 0 || dev->sm_count < 2 || !f16) return false;
-    const char* e = getenv("BM_SPARSE_PAIR");
-    if (e && atoi(e) == 0) return false;
+    if (opt(OPT_SPARSE_PAIR) == 0) return false;
     return static_cast<long long>(ceil_div(R, 256)) * ceil_div(Cn, SpPairCfg<true>::BN) >= dev->sm_count;
 }
 
-// BM_SPARSE_PAIR=0 keeps large sparse-weight problems on the single-CTA kernel (testing hook)
-static bool sparse_pair_enabled() {
-    const char* e = getenv("BM_SPARSE_PAIR");
-    return !e || atoi(e) != 0;
-}
+// option "sparse_pair" = 0 keeps large sparse-weight problems on the single-CTA kernel (testing hook)
+static bool sparse_pair_enabled() { return opt(OPT_SPARSE_PAIR) != 0; }
 
 // mode 0: sparse operand on the left, out[r][c];  mode 1: sparse weights, out[c][r]
 static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* meta_tiled, const int8_t* Dn,
@@ -454,11 +407,11 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
         // layer): column tiles fastest, so the pairs working at the same time share a block of weights and
         // every block leaves HBM once — N = 28672, K = 8192 (147 MB): 3001 -> 3662 TOPS at 1024 tokens,
         // 3305 -> 4142 at 2048.  Otherwise row blocks fastest (8192^3: 4284 vs 3722 TOPS).
-        // BM_SPARSE_COL_FIRST=0/1 overrides.
+        // Option "sparse_col_first" = 0/1 overrides.
         {
             const double w_bytes = 0.625 * static_cast<double>(R) * K, x_bytes = static_cast<double>(Cn) * K;
             p.col_first = (w_bytes > 96e6 && 2.0 * x_bytes <= w_bytes) ? 1 : 0;
-            if (const char* e = getenv("BM_SPARSE_COL_FIRST")) p.col_first = atoi(e) != 0;
+            if (opt(OPT_SPARSE_COL_FIRST) >= 0) p.col_first = opt(OPT_SPARSE_COL_FIRST) != 0;
         }
         const int pair_tiles = p.tiles_r * p.tiles_c;
         const int max_pairs = dev->sm_count / 2;
@@ -522,36 +475,36 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
     int grid = num_tiles < resident ? num_tiles : resident;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    // Row-balanced tiles for the decode shapes (packed weights, all tokens in one column tile): whole
-    // 128-row tiles would give some SMs two tiles and others one (224 tiles on 148 SMs); dealing the
-    // rows out in multiples of 8 keeps every SM streaming the same number of bytes.  BM_ROW_BALANCED=0
-    // switches it off.
+    // Stream-K: the (tile, K block) units are dealt out evenly instead of whole tiles; a tile shared by
+    // several CTAs is finished by whichever arrives last (exact int32 sums parked in library scratch).
+    // Automatic (option "stream_k" = -1) for decode shapes whose row tiles would fill fewer than half of the
+    // CTA slots — a column slab of an N-split layer: 3584 channels are 28 tiles for 296 slots; every CTA then
+    // streams ~3 K blocks of one tile and fetches only that K range of the activations.  With enough row
+    // tiles whole tiles are kept: at N = 28672, K = 8192 stream-K was measured 1 % slower (33.5 vs 33.1 us),
+    // the parked sums add a dependent chain at the end.  1 forces it wherever it applies, 0 forbids it.
     p.sparse_rows = R;
-    if (mode == 1 && packed && p.tiles_c == 1 && num_tiles % resident != 0 && R >= 8 * resident) {
-        const char* e = getenv("BM_ROW_BALANCED");
-        if (!e || atoi(e) != 0) {
-            p.row_balanced = 1;
-            grid = resident;
-        }
+    const long long units = static_cast<long long>(num_tiles) * p.k_blocks;
+    const int sk = opt(OPT_STREAM_K);
+    const bool sk_auto = sk < 0 && mode == 1 && p.tiles_c == 1 && 2 * num_tiles <= resident && p.k_blocks >= 4;
+    if ((sk > 0 || sk_auto) && units >= 2) {
+        grid = units < resident ? static_cast<int>(units) : resident;
+        const int epi_warps = bn >= 128 ? 8 : 4;
+        const size_t slice_ints = static_cast<size_t>(bn >= 128 ? bn / 2 : (bn == 64 ? 64 : 32)) * 32;
+        const size_t ws_bytes = static_cast<size_t>(grid) * 2 * epi_warps * slice_ints * sizeof(int32_t);
+        if (int rc = ensure_split_k(dev, ws_bytes, static_cast<size_t>(num_tiles) * epi_warps)) return rc;
+        p.stream_k = 1;
+        p.sk_workspace = static_cast<int32_t*>(dev->sk_workspace);
+        p.sk_counters = dev->sk_counters;
     }
 
-    // Stream-K (BM_STREAM_K=1): the (tile, K block) units are dealt out evenly instead of whole tiles.
-    // Off by default: on the decode shapes it was measured 1 % slower than whole tiles (33.5 vs
-    // 33.1 us at N=28672, K=8192) because the parked partial sums add a dependent chain at the end.
-    {
-        const long long units = static_cast<long long>(num_tiles) * p.k_blocks;
-        const char* force = getenv("BM_STREAM_K");
-        const bool want = force && atoi(force) != 0 && units >= 2 && !p.row_balanced;
-        if (want) {
-            grid = units < resident ? static_cast<int>(units) : resident;
-            const int epi_warps = bn >= 128 ? 8 : 4;
-            const size_t slice_ints = static_cast<size_t>(bn >= 128 ? bn / 2 : (bn == 64 ? 64 : 32)) * 32;
-            const size_t ws_bytes = static_cast<size_t>(grid) * 2 * epi_warps * slice_ints * sizeof(int32_t);
-            if (int rc = ensure_split_k(dev, ws_bytes, static_cast<size_t>(num_tiles) * epi_warps)) return rc;
-            p.stream_k = 1;
-            p.sk_workspace = static_cast<int32_t*>(dev->sk_workspace);
-            p.sk_counters = dev->sk_counters;
-        }
+    // Row-balanced tiles for the decode shapes (packed weights, all tokens in one column tile): whole
+    // 128-row tiles would give some SMs two tiles and others one (224 tiles on 148 SMs); dealing the
+    // rows out in multiples of 8 keeps every SM streaming the same number of bytes.  Option
+    // "row_balanced" = 0 switches it off.
+    if (!p.stream_k && mode == 1 && packed && p.tiles_c == 1 && num_tiles % resident != 0 && R >= 8 * resident &&
+        opt(OPT_ROW_BALANCED) != 0) {
+        p.row_balanced = 1;
+        grid = resident;
     }
 
 #define BM_SP(BNV, MN, TR, E) return launch_sparse_inst<BNV, MN, TR, E>(map_s, map_d, p, grid, stream)
@@ -621,13 +574,8 @@ static int launch_hsparse(const CUtensorMap& ms, const CUtensorMap& md, const Sp
                           cudaStream_t stream) {
     using Cfg = SparseCfg<BN>;
     auto kern = igemm_sparse_kernel<BN, true, false, EPI_I32, false, true>;
-    static bool configured[kMaxDevices] = {};
-    int dev = 0;
-    BM_CUDA_TRY(cudaGetDevice(&dev));
-    if (!configured[dev]) {
-        BM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        configured[dev] = true;
-    }
+    static ConfiguredFlags flags;
+    if (int rc = ensure_smem_limit(flags, kern, Cfg::SMEM_BYTES)) return rc;
     BM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, 1, ms, md, p));
     return BM_OK;
 }
@@ -656,11 +604,37 @@ int bm_w8a8_f16(const int8_t* X, const int8_t* W, uint16_t* D, const float* sa_m
     return dense_gemm(EPI_F16_ROWCOL, X, W, D, M, N, K, ldd, w_layout, 1.f, sa_m, sw_n, nullptr, stream);
 }
 
-int bm_w8a8_f16_gather(const int8_t* X, const int8_t* W, uint16_t* const* D_peers, int n_peers, const float* sa_m,
-                       const float* sw_n, int M, int N, int K, int64_t ldd, int w_layout, void* stream) {
+int bm_w8a8_f16_gather(const int8_t* X, const int8_t* W, uint16_t* const* D_peers, int n_peers, int self_index,
+                       const float* sa_m, const float* sw_n, int M, int N, int K, int64_t ldd, int w_layout,
+                       void* stream) {
     if (!D_peers || n_peers <= 0) return fail_msg(BM_ERR_NULL, "no gather destinations given");
-    return dense_gemm(EPI_F16_ROWCOL, X, W, D_peers[0], M, N, K, ldd, w_layout, 1.f, sa_m, sw_n, nullptr, stream,
-                      reinterpret_cast<void* const*>(D_peers), n_peers);
+    if (self_index < -1 || self_index >= n_peers) return fail_msg(BM_ERR_SHAPE, "self_index must be -1 or an index into D_peers");
+    return dense_gemm(EPI_F16_ROWCOL, X, W, D_peers[self_index < 0 ? 0 : self_index], M, N, K, ldd, w_layout, 1.f, sa_m,
+                      sw_n, nullptr, stream, reinterpret_cast<void* const*>(D_peers), n_peers, self_index);
+}
+
+int bm_gather_slab_f16(uint16_t* const* D_peers, int n_peers, int self_index, int M, int n_len, int64_t ldd, void* stream) {
+    if (!D_peers || n_peers <= 0 || n_peers > kGatherMaxPeers) return fail_msg(BM_ERR_NULL, "1 to 8 gather destinations are needed");
+    if (self_index < 0 || self_index >= n_peers) return fail_msg(BM_ERR_SHAPE, "self_index must be an index into D_peers");
+    if (M <= 0 || n_len <= 0 || ldd < n_len) return fail_msg(BM_ERR_SHAPE, "M, n_len must be positive and ldd >= n_len");
+    if (n_len % 8 != 0 || ldd % 8 != 0) return fail_msg(BM_ERR_ALIGN, "slab width and pitch must be multiples of 8 elements (16 bytes)");
+    GatherDests dests{};
+    for (int d = 0; d < n_peers; ++d) {
+        if (!D_peers[d] || !aligned16(D_peers[d])) return fail_msg(BM_ERR_ALIGN, "gather destinations must be 16-byte aligned");
+        dests.ptr[d] = D_peers[d];
+    }
+    if (n_peers == 1) return BM_OK;
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    const int row_bytes = n_len * 2;
+    const long long tiles = static_cast<long long>((M + 7) / 8) * ((row_bytes + 511) / 512);
+    const long long cap = static_cast<long long>(dev->sm_count) * 4;
+    const int gbs = opt(OPT_GATHER_GBS);
+    const unsigned cost = gbs > 0 ? static_cast<unsigned>((4096.0 * 16.0) / gbs + 0.5) : 0u;
+    gather_slab_kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kGatherThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        dests, n_peers, self_index, M, row_bytes, static_cast<long long>(ldd) * 2, dev->link_clock, cost);
+    BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
 }
 
 int bm_quantize_rows_f16(const uint16_t* X_f16, int8_t* X_q, float* scale_m, int M, int K, void* stream) {
@@ -872,6 +846,39 @@ int bm_last_device_status(int* code) {
         // an aborted stream-K launch may have left arrival counters half-way
         if (dev->sk_counters) BM_CUDA_TRY(cudaMemset(dev->sk_counters, 0, dev->sk_counter_ints * sizeof(int)));
     }
+    // launches of the no-alloc entry point record their give-ups in a word of their own
+    int fixed = 0;
+    if (int rc = noalloc_read_status(&fixed)) return rc;
+    if (*code == 0) *code = fixed;
+    return BM_OK;
+}
+
+int bm_set_option(const char* name, int value) {
+    if (!name) return fail_msg(BM_ERR_NULL, "option name is NULL");
+    for (int i = 0; i < OPT_COUNT; ++i)
+        if (strcmp(name, option_specs()[i].name) == 0) {
+            option_values()[i].store(value, std::memory_order_relaxed);
+            return BM_OK;
+        }
+    return fail_msg(BM_ERR_LAYOUT, "unknown option name");
+}
+
+int bm_get_option(const char* name, int* value) {
+    if (!name || !value) return fail_msg(BM_ERR_NULL, "pointer is NULL");
+    for (int i = 0; i < OPT_COUNT; ++i)
+        if (strcmp(name, option_specs()[i].name) == 0) {
+            *value = opt(i);
+            return BM_OK;
+        }
+    return fail_msg(BM_ERR_LAYOUT, "unknown option name");
+}
+
+int bm_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses, uint64_t* entries) {
+    MapCache& c = map_cache();
+    std::lock_guard<std::mutex> lock(c.mutex);
+    if (hits) *hits = c.hits.load();
+    if (misses) *misses = c.misses.load();
+    if (entries) *entries = c.maps.size();
     return BM_OK;
 }
 
@@ -894,6 +901,11 @@ int bm_selftest_bounded_wait(unsigned limit_us, int* outcome) {
 const char* bm_last_error_string(void) { return error_buffer(); }
 
 void bm_shutdown(void) {
+    {
+        MapCache& c = map_cache();
+        std::lock_guard<std::mutex> lock(c.mutex);
+        c.maps.clear();
+    }
     std::lock_guard<std::mutex> lock(state_mutex());
     for (int d = 0; d < kMaxDevices; ++d) {
         DeviceState& s = device_states()[d];
@@ -914,11 +926,3 @@ void bm_shutdown(void) {
 const char* bm_version(void) { return "0.1"; }
 
 }  // extern "C"
-
-#ifdef BM_TILE_TRACE
-// developer build only: copy the pair kernel's time stamps to the host
-extern "C" int bm_debug_read_trace(void* dst, size_t bytes) {
-    if (bytes > sizeof(bm::g_pair_trace)) bytes = sizeof(bm::g_pair_trace);
-    return cudaMemcpyFromSymbol(dst, bm::g_pair_trace, bytes) == cudaSuccess ? 0 : -1;
-}
-#endif

@@ -13,8 +13,12 @@
 //   * the re-tiled metadata must fit BM_NOALLOC_META_BYTES (2 MiB): ceil(M/128) * ceil(K/256)
 //     * 4096 bytes, i.e. up to M = K = 4096 (or any M*K of that area in whole tiles).  Larger
 //     problems are rejected with BM_ERR_TOO_LARGE before anything is launched;
-//   * every GPU that loads the library carries the 2 MiB array (plus a 4-byte status word)
-//     until the process exits, whether or not this entry point is ever called;
+//   * the 2 MiB array (plus two status words) is part of the library's device image: a GPU holds it
+//     from the moment the CUDA runtime loads that image on it until the process exits.  With the
+//     runtime's default lazy loading that moment is this entry point's FIRST CALL on the device
+//     (with CUDA_MODULE_LOADING=EAGER it is context creation).  A process whose pool is about to
+//     claim the whole device must therefore make one call — any small problem — BEFORE the pool
+//     takes the memory, or run with eager loading; afterwards no call reserves anything;
 //   * all calls on a device share the one array.  It still holds the previous call's metadata
 //     when the next call starts; that is harmless because the packing kernel rewrites every
 //     byte the GEMM will read before the GEMM starts (same stream, so ordered), so nothing has
@@ -25,6 +29,11 @@
 // with that device current, asks the runtime for the array's device address
 // (cudaGetSymbolAddress) and raises the kernel's shared-memory limit; later calls reuse the
 // cached address.  Make that first call outside any stream capture.
+//
+// Errors inside a launch: the GEMM's bounded waits record a give-up in g_noalloc_status, a word
+// of this file (not the cudaMalloc'ed word of the other entry points).  Read and clear it with
+// bm_noalloc_last_device_status, which allocates nothing either; bm_last_device_status reports
+// it too, but creates the library's regular per-device state on first use (a 4-byte cudaMalloc).
 #include <cstdlib>
 
 #include "host_common.cuh"
@@ -37,6 +46,7 @@ namespace bm {
 // Fixed scratch for the tiled metadata and the timeout status of this entry point's launches.
 static __device__ __align__(256) unsigned char g_noalloc_meta[BM_NOALLOC_META_BYTES];
 static __device__ int g_noalloc_status;
+static __device__ int g_noalloc_selftest;      // outcome word of bm_noalloc_selftest_bounded_wait
 
 // Reference uint32 metadata words -> tiled order, written straight into the fixed array
 // (device code may name the array directly).  Same mapping as bm_sp_pack_meta with BM_META_REF:
@@ -69,8 +79,14 @@ struct NoAllocDevice {
     bool ready = false;
     unsigned char* meta = nullptr;     // device address of g_noalloc_meta on this device
     int* status = nullptr;             // device address of g_noalloc_status on this device
+    int* selftest = nullptr;           // device address of g_noalloc_selftest on this device
     int sm_count = 0;
 };
+
+static NoAllocDevice* noalloc_devices() {
+    static NoAllocDevice devices[kMaxDevices];
+    return devices;
+}
 
 static std::mutex& noalloc_mutex() {
     static std::mutex m;
@@ -79,12 +95,11 @@ static std::mutex& noalloc_mutex() {
 
 // Once per device, with that device current: resolve the device addresses of the fixed arrays.
 static int noalloc_device(NoAllocDevice** out) {
-    static NoAllocDevice devices[kMaxDevices];
     int dev = 0;
     BM_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return fail_msg(BM_ERR_CUDA, "device index out of range");
     std::lock_guard<std::mutex> lock(noalloc_mutex());
-    NoAllocDevice& d = devices[dev];
+    NoAllocDevice& d = noalloc_devices()[dev];
     if (!d.ready) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_meta);
@@ -93,6 +108,9 @@ static int noalloc_device(NoAllocDevice** out) {
         e = cudaGetSymbolAddress(&p, g_noalloc_status);
         if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(g_noalloc_status)");
         d.status = static_cast<int*>(p);
+        e = cudaGetSymbolAddress(&p, g_noalloc_selftest);
+        if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(g_noalloc_selftest)");
+        d.selftest = static_cast<int*>(p);
         BM_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
         BM_CUDA_TRY(cudaFuncSetAttribute(igemm_sparse_kernel<128, true, false, EPI_F32_TENSOR>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SparseCfg<128>::SMEM_BYTES));
@@ -102,9 +120,60 @@ static int noalloc_device(NoAllocDevice** out) {
     return BM_OK;
 }
 
+// Declared in host_common.cuh.  The caller has synchronised the device.  Nothing is allocated:
+// cudaMemcpy / cudaMemset on an existing address, and only when this file's set-up has run here.
+int noalloc_read_status(int* code) {
+    *code = 0;
+    int dev = 0;
+    BM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail_msg(BM_ERR_CUDA, "device index out of range");
+    std::lock_guard<std::mutex> lock(noalloc_mutex());
+    const NoAllocDevice& d = noalloc_devices()[dev];
+    if (!d.ready) return BM_OK;
+    BM_CUDA_TRY(cudaMemcpy(code, d.status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*code != 0) BM_CUDA_TRY(cudaMemset(d.status, 0, sizeof(int)));
+    return BM_OK;
+}
+
+// A wait that nothing satisfies, with a short limit, recording into the status word it is given:
+// the give-up path of the pipeline waits, exercised without hanging or faulting anything.
+static __global__ void noalloc_selftest_kernel(int* status, unsigned long long limit_ns, int* returned) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool ok = bounded_wait(smem_u32(&bar), 0, &abort_flag, status, DEV_TIMEOUT_DRAIN, limit_ns);
+        *returned = ok ? 1 : 2;                     // 2 = gave up cleanly
+    }
+}
+
 }  // namespace bm
 
 using namespace bm;
+
+extern "C" int bm_noalloc_last_device_status(int* code) {
+    if (!code) return fail_msg(BM_ERR_NULL, "code pointer is NULL");
+    BM_CUDA_TRY(cudaDeviceSynchronize());
+    return noalloc_read_status(code);
+}
+
+extern "C" int bm_noalloc_selftest_bounded_wait(unsigned limit_us, int* outcome) {
+    if (!outcome) return fail_msg(BM_ERR_NULL, "outcome pointer is NULL");
+    if (limit_us == 0 || limit_us > 2000000u) return fail_msg(BM_ERR_SHAPE, "limit must be 1 us .. 2 s");
+    NoAllocDevice* dev = nullptr;
+    if (int rc = noalloc_device(&dev)) return rc;
+    BM_CUDA_TRY(cudaMemset(dev->selftest, 0, sizeof(int)));
+    noalloc_selftest_kernel<<<1, 32>>>(dev->status, static_cast<unsigned long long>(limit_us) * 1000ull, dev->selftest);
+    BM_CUDA_TRY(cudaGetLastError());
+    BM_CUDA_TRY(cudaDeviceSynchronize());
+    BM_CUDA_TRY(cudaMemcpy(outcome, dev->selftest, sizeof(int), cudaMemcpyDeviceToHost));
+    return BM_OK;
+}
 
 extern "C" int bm_igemm_sparse_f32_noalloc(const int8_t* A_comp, const int8_t* B, float* C, const uint32_t* meta, int M,
                                            int N, int K, float scale_a, float scale_b, void* stream_v) {

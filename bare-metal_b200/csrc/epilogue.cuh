@@ -251,27 +251,44 @@ struct OutMaps {
     CUtensorMap m[kMaxOutMaps];
 };
 
-// Where the 32-column chunks of a drain come from: tensor memory (asynchronous loads, waited for
-// just before use) or the parked partial sums of a split tile (added up on the fly).
+// Pacing of stores that leave the GPU over NVLink.  Measured on two B200s: when SMs offer peer stores faster
+// than the link takes them (~770 GB/s per direction), the stores back up towards the SMs and the
+// operand LOADS of the same SMs collapse from ~23 TB/s to ~1 TB/s until the backlog is gone — TMA stores
+// and plain st.global alike — so an unpaced fused gather computes OR sends, never both.  Offered at up to
+// ~720 GB/s the same stores leave the loads untouched.  All CTAs of a GPU therefore draw their remote
+// stores from one token bucket: a virtual clock in global memory (1/16 ns units) that every remote
+// 4 KiB store advances by `cost`; a store waits until the wall clock reaches its slot.  The bucket holds
+// 1 us of credit, so an idle link takes a short burst at once.  The wait is bounded (2 ms): pacing is an
+// optimisation, never a condition for correctness.
+struct StorePace {
+    unsigned long long* clock;      // shared by every launch on this GPU
+    unsigned cost;                  // virtual-clock units per remote box store; 0 = no pacing
+    unsigned remote_mask;           // bit d set: destination d is another GPU's memory
+    int first;                      // destination served first (the GPU's own buffer); the others follow in ring order
+};
+
+__device__ __forceinline__ unsigned long long pace_now() {
+    return (global_timer_ns() & 0x00FFFFFFFFFFFFFFull) << 4;
+}
+__device__ __forceinline__ void pace_remote_store(unsigned long long* clock, unsigned cost) {
+    constexpr unsigned long long kCredit = 16ull * 1000;            // 1 us
+    constexpr unsigned long long kGiveUp = 16ull * 2000000;         // 2 ms
+    unsigned long long now = pace_now();
+    atomicMax(clock, now > kCredit ? now - kCredit : 0ull);
+    const unsigned long long slot = atomicAdd(clock, static_cast<unsigned long long>(cost));
+    if (slot > now + 16ull * 1000000000) {                          // a clock from another epoch: restart it
+        atomicExch(clock, now);
+        return;
+    }
+    const unsigned long long t0 = now;
+    while (now < slot && now - t0 < kGiveUp) now = pace_now();
+}
+
+// The 32-column chunks of a drain come from tensor memory: asynchronous loads, waited for just before use.
 struct TmemSource {
     uint32_t taddr;
     __device__ __forceinline__ void issue(int c, uint32_t (&r)[32]) const { tmem_ld_32x32(taddr + c * 32, r); }
     __device__ __forceinline__ void wait() const { tmem_ld_wait(); }
-};
-template <class PartPtr>
-struct ParkedSource {
-    PartPtr part_ptr;      // part index -> this warp's slice of that part
-    int parts, lane;
-    __device__ __forceinline__ void issue(int c, uint32_t (&r)[32]) const {
-#pragma unroll
-        for (int k = 0; k < 32; ++k) r[k] = 0;
-        for (int part = 0; part < parts; ++part) {
-            const int32_t* s = part_ptr(part) + c * 32 * 32 + lane;
-#pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] += static_cast<uint32_t>(__ldcg(s + k * 32));
-        }
-    }
-    __device__ __forceinline__ void wait() const {}
 };
 
 // NBUF staging strips per warp (1 or 2), used round-robin over the boxes of all tiles (`box_count`
@@ -280,7 +297,8 @@ struct ParkedSource {
 template <int EPI, int NC, int NBUF, class Source>
 __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const CUtensorMap* maps, int n_maps, const Source& src,
                                                int row0, int lane, int col0, const EpiStrip<NC>* strip, float lane_s,
-                                               uint32_t stage_smem0, uint32_t& box_count, int col_limit) {
+                                               uint32_t stage_smem0, uint32_t& box_count, int col_limit,
+                                               const StorePace& pace = StorePace{nullptr, 0u, 0u, 0}) {
     using T = typename OutType<EPI>::type;
     static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
     constexpr int CHUNKS = NC / 32;
@@ -333,7 +351,12 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const CU
             fence_proxy_async_smem();                        // generic-proxy writes -> visible to the TMA engine
             __syncwarp();
             if (lane == 0) {
-                for (int d = 0; d < n_maps; ++d) tma_store_2d(maps + d, stage_smem, box_c0, row0);
+                for (int i = 0; i < n_maps; ++i) {
+                    int d = pace.first + i;
+                    if (d >= n_maps) d -= n_maps;
+                    if (pace.cost != 0 && ((pace.remote_mask >> d) & 1u)) pace_remote_store(pace.clock, pace.cost);
+                    tma_store_2d(maps + d, stage_smem, box_c0, row0);
+                }
                 bulk_commit_group();
             }
             ++box_count;
@@ -345,9 +368,10 @@ template <int EPI, int NC, int NBUF>
 __device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, const CUtensorMap* maps, int n_maps,
                                                       uint32_t taddr, int row0, int lane, int col0,
                                                       const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem0,
-                                                      uint32_t& box_count, int col_limit) {
+                                                      uint32_t& box_count, int col_limit,
+                                                      const StorePace& pace = StorePace{nullptr, 0u, 0u, 0}) {
     drain_tma_from<EPI, NC, NBUF>(p, maps, n_maps, TmemSource{taddr}, row0, lane, col0, strip, lane_s, stage_smem0,
-                                  box_count, col_limit);
+                                  box_count, col_limit, pace);
 }
 
 }  // namespace bm

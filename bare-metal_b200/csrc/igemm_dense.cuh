@@ -55,19 +55,14 @@ struct DenseParams {
     int tiles_m, tiles_n, k_blocks;
     int* status;
     int n_out;                 // number of output destinations in the OutMaps argument (1 unless gathering)
-    // tail split (CTA-pair kernel): tiles [0, tail_first) run whole, wave after wave; each of the
-    // remaining tiles is cut into `tail_split` K ranges handled by different pairs, so the last,
-    // partly filled wave takes 1/tail_split of a tile time.  Partial sums meet in sk_workspace and
-    // the part that arrives last (per epilogue warp, counted in sk_counters) finishes the tile.
-    int tail_first, tail_split;
-    // half-height tail (CTA-pair kernel): the tiles of a partly filled last wave are computed as two
-    // 128 x 256 halves by different pairs — no reduction, just shorter tiles for the idle pairs.
-    int tail_narrow;
+    StorePace pace;            // gathering: which destinations are remote and how their stores are paced
+    // half-height tail (CTA-pair kernel): tiles [0, tail_first) run whole, wave after wave; the tiles of
+    // the partly filled last wave are computed as two 128 x 256 halves by different pairs — no
+    // reduction, just shorter units for pairs that would otherwise idle.
+    int tail_first, tail_narrow;
     // tile order of the CTA-pair kernel: 0 = row tiles fastest over the whole matrix; G > 0 = bands of G
     // row tiles, inside a band row tiles fastest (a wave then touches G row tiles x pairs/G column tiles)
     int group_m;
-    int* sk_counters;          // [tail tiles][2 CTAs][epilogue warps], zero between launches
-    int32_t* sk_workspace;     // [tail tiles][tail_split][2 CTAs][epilogue warps][NC x 32]
 };
 
 // (row tile, column tile) of linear tile index `tile` under DenseParams::group_m
@@ -250,7 +245,7 @@ igemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 if (p.epi.tma_ok) {
                     drain_accumulator_tma<EPI, Cfg::NC, 1>(p.epi, maps_out.m, p.n_out, taddr, m0 + quarter * 32, lane, n0, strip,
                                                            lane_s, smem_base + Cfg::STORE_OFFSET + (warp - 2) * kStoreBoxBytes,
-                                                           box_count, p.epi.cols);
+                                                           box_count, p.epi.cols, p.pace);
                     stored = true;
                 }
             }

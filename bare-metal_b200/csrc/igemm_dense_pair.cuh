@@ -42,50 +42,30 @@ constexpr int kPairNC = kPairBN / 2;                // columns drained per epilo
 constexpr int kPairStripOffset = kPairBarOffset + (2 * kPairStages + 5) * 8 + 16;
 constexpr int kPairSmemBytes = kPairStripOffset + kEpiWarps * (int)sizeof(EpiStrip<kPairNC>) + 1024;
 
-// Work of one CTA pair: whole tiles pair, pair+P, ... below `tail_first`, then (if the tail is
-// split) one K range of one tail tile.
+// Work of one CTA pair: whole tiles pair, pair+P, ... below `tail_first`, then (half-height tail) one
+// 128-row half of one tile of the partly filled last wave.
 struct PairWork {
-    int tile, kb0, kb1, part;           // part < 0: the whole K range
+    int tile;
     int nhalf;                          // < 0: all 256 rows; 0 / 1: rows [128 nhalf, +128) of the tile only (a half-height unit)
 };
 struct PairWorkIter {
-    int next_tile, pairs, tiles, tail_first, split, k_blocks, pair;
+    int next_tile, pairs, tiles, tail_first, pair;
     bool tail_done, narrow;
-    __device__ PairWorkIter(int pair_, int pairs_, int tiles_, int k_blocks_, int tail_first_, int split_,
-                            bool narrow_ = false)
-        : next_tile(pair_), pairs(pairs_), tiles(tiles_),
-          tail_first((split_ > 1 || narrow_) ? tail_first_ : tiles_), split(split_), k_blocks(k_blocks_), pair(pair_),
+    __device__ PairWorkIter(int pair_, int pairs_, int tiles_, int tail_first_, bool narrow_)
+        : next_tile(pair_), pairs(pairs_), tiles(tiles_), tail_first(narrow_ ? tail_first_ : tiles_), pair(pair_),
           tail_done(false), narrow(narrow_) {}
     __device__ bool next(PairWork& w) {
         w.nhalf = -1;
         if (next_tile < tail_first) {
             w.tile = next_tile;
-            w.kb0 = 0;
-            w.kb1 = k_blocks;
-            w.part = -1;
             next_tile += pairs;
             return true;
         }
         if (narrow && !tail_done) {
             tail_done = true;
-            if (pair < (tiles - tail_first) * 2) {                   // pair u takes column half u % 2 of tail tile u / 2
+            if (pair < (tiles - tail_first) * 2) {                   // pair u takes row half u % 2 of tail tile u / 2
                 w.tile = tail_first + pair / 2;
                 w.nhalf = pair % 2;
-                w.kb0 = 0;
-                w.kb1 = k_blocks;
-                w.part = -1;
-                return true;
-            }
-            return false;
-        }
-        if (split > 1 && !tail_done) {
-            tail_done = true;
-            const int unit = pair;                                   // pair u takes part u % split of tail tile u / split
-            if (unit < (tiles - tail_first) * split) {
-                w.tile = tail_first + unit / split;
-                w.part = unit % split;
-                w.kb0 = static_cast<int>(static_cast<long long>(k_blocks) * w.part / split);
-                w.kb1 = static_cast<int>(static_cast<long long>(k_blocks) * (w.part + 1) / split);
                 return true;
             }
         }
@@ -93,20 +73,7 @@ struct PairWorkIter {
     }
 };
 
-// TAIL_SPLIT compiles the parked-partial-sum path in; the default instantiation leaves it out (it
-// costs registers in the drain loop even when never taken).
-#ifdef BM_TILE_TRACE
-// Developer build only (-DBM_TILE_TRACE): per pair and tile, %globaltimer stamps of the MMA lane and of
-// one epilogue warp, read back with bm_debug_read_trace().
-constexpr int kTraceTiles = 8, kTraceSlots = 8;
-__device__ unsigned long long g_pair_trace[74][kTraceTiles][kTraceSlots];
-#define BM_TRACE(pair, t, slot, val) \
-    do { if ((pair) < 74 && (t) < kTraceTiles) g_pair_trace[pair][t][slot] = (val); } while (0)
-#else
-#define BM_TRACE(pair, t, slot, val) do {} while (0)
-#endif
-
-template <bool B_MN, int EPI, bool TAIL_SPLIT = false>
+template <bool B_MN, int EPI>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_a_short, const __grid_constant__ OutMaps maps_out,
@@ -169,19 +136,17 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             prefetch_tensormap(&map_b);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
-                              p.tail_narrow != 0);
+            PairWorkIter work(pair, num_pairs, num_tiles, p.tail_first, p.tail_narrow != 0);
             PairWork w;
             while (ok && work.next(w)) {
-                const int tile = w.tile;
                 int tm, tn;
-                pair_tile_coords(p, tile, tm, tn);
+                pair_tile_coords(p, w.tile, tm, tn);
                 const int m0 = tm * 256 + static_cast<int>(rank) * kBM;
                 // half-height unit: 128 rows of the tile, 64 per CTA (an M = 128 pair MMA); B as for a whole tile
                 const bool narrow = w.nhalf >= 0;
                 const int n0 = tn * kPairBN + static_cast<int>(rank) * kPairHalfN;
                 const int m0s = tm * 256 + w.nhalf * 128 + static_cast<int>(rank) * 64;
-                for (int kb = w.kb0; kb < w.kb1; ++kb) {
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
                     const uint32_t leader_full = mapa_shared(full_bar(stage), 0);
@@ -203,36 +168,20 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             constexpr uint32_t idesc_narrow = make_idesc_i8(128, kPairBN, B_MN, false);   // 64 rows per CTA
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
-                              p.tail_narrow != 0);
+            PairWorkIter work(pair, num_pairs, num_tiles, p.tail_first, p.tail_narrow != 0);
             PairWork w;
-#ifdef BM_TILE_TRACE
-            int trace_t = 0;
-#endif
             while (ok && work.next(w)) {
-                BM_TRACE(pair, trace_t, 0, global_timer_ns());
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
                 tc_fence_after_sync();
-                BM_TRACE(pair, trace_t, 1, global_timer_ns());
-#ifdef BM_TILE_TRACE
-                unsigned long long wait_ns = 0;
-#endif
                 const uint32_t d_tmem = tmem_base + acc * kPairBN;
                 const uint32_t idesc = w.nhalf >= 0 ? idesc_narrow : idesc_full;
-                for (int kb = w.kb0; kb < w.kb1; ++kb) {
-#ifdef BM_TILE_TRACE
-                    const unsigned long long tw0 = global_timer_ns();
-#endif
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-#ifdef BM_TILE_TRACE
-                    if (kb == w.kb0) BM_TRACE(pair, trace_t, 2, global_timer_ns());
-                    else wait_ns += global_timer_ns() - tw0;
-#endif
                     const uint32_t a_addr = a_smem0 + stage * kABytes;
                     const uint32_t b_addr = b_smem0 + stage * kPairBBytes;
 #pragma unroll
@@ -241,7 +190,7 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const uint64_t b_desc =
                             B_MN ? make_smem_desc(b_addr + ks * (kUmmaK * 128), 128 * kBK, 1024, SWIZZLE_128B_DESC)
                                  : make_smem_desc(b_addr + ks * kUmmaK, 0, 1024, SWIZZLE_128B_DESC);
-                        mma_i8_pair(d_tmem, a_desc, b_desc, idesc, (kb != w.kb0 || ks != 0) ? 1u : 0u);
+                        mma_i8_pair(d_tmem, a_desc, b_desc, idesc, (kb | ks) != 0 ? 1u : 0u);
                     }
                     tc_commit_pair(empty_bar(stage));                       // this CTA's producer
                     tc_commit_pair(mapa_shared(empty_bar(stage), 1));       // the peer's producer
@@ -250,11 +199,6 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (!ok) break;
                 tc_commit_pair(acc_full_bar(acc));
                 tc_commit_pair(mapa_shared(acc_full_bar(acc), 1));
-#ifdef BM_TILE_TRACE
-                BM_TRACE(pair, trace_t, 3, global_timer_ns());
-                BM_TRACE(pair, trace_t, 4, wait_ns);
-                ++trace_t;
-#endif
                 acc ^= 1u;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -270,16 +214,11 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int half = (warp - 2) >> 2;
         EpiStrip<kPairNC>* strip = reinterpret_cast<EpiStrip<kPairNC>*>(smem_gen + kPairStripOffset) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0, box_count = 0;
-        PairWorkIter work(pair, num_pairs, num_tiles, p.k_blocks, p.tail_first, TAIL_SPLIT ? p.tail_split : 1,
-                              p.tail_narrow != 0);
+        PairWorkIter work(pair, num_pairs, num_tiles, p.tail_first, p.tail_narrow != 0);
         PairWork w;
-#ifdef BM_TILE_TRACE
-        int trace_e = 0;
-#endif
         while (work.next(w)) {
-            const int tile = w.tile;
             int tm, tn;
-            pair_tile_coords(p, tile, tm, tn);
+            pair_tile_coords(p, w.tile, tm, tn);
             const int m0 = tm * 256 + static_cast<int>(rank) * kBM;
             // Whole tile: lanes = the CTA's 128 rows, this warp drains TMEM columns [128 half, +128).
             // Half-height unit (M = 128 on the pair): the CTA's 64 rows sit in lanes 0-63 for output columns
@@ -296,65 +235,21 @@ igemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
             tc_fence_after_sync();
-#ifdef BM_TILE_TRACE
-            if (warp == 2 && lane == 0 && rank == 0) BM_TRACE(pair, trace_e, 5, global_timer_ns());
-#endif
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kPairBN +
                                    (narrow ? half * 64 : half * kPairNC);
             const uint32_t my_stage = smem_base + kPairStoreOffset + (warp - 2) * kPairStoreBufs * kStoreBoxBytes;
-            if (!TAIL_SPLIT || w.part < 0) {
-                if (p.epi.tma_ok)
-                    drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out.m, p.n_out, taddr, row_base, lane,
-                                                                        n0, strip, lane_s, my_stage, box_count, col_limit);
-                else
-                    drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, col_limit, strip, lane_s);
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
-            } else if constexpr (TAIL_SPLIT) {
-                // one K range of a split tail tile: park the raw sums; whoever completes the slice finishes it
-                constexpr int SLICE = kPairNC * 32;
-                const int tail_idx = tile - p.tail_first;
-                const int slice_id = static_cast<int>(rank) * kEpiWarps + (warp - 2);
-                auto part_of = [&](int part) -> int32_t* {
-                    return p.sk_workspace +
-                           ((static_cast<size_t>(tail_idx) * p.tail_split + part) * 2 * kEpiWarps + slice_id) * SLICE;
-                };
-                park_accumulator<kPairNC>(taddr, part_of(w.part), lane);
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
-                __threadfence();
-                int last = 0;
-                int* counter = p.sk_counters + tail_idx * 2 * kEpiWarps + slice_id;
-                if (lane == 0) {
-                    last = (atomicAdd(counter, 1) == p.tail_split - 1);
-                    if (last) *counter = 0;
-                }
-                last = __shfl_sync(0xFFFFFFFFu, last, 0);
-                if (last) {
-                    __threadfence();
-                    auto ptr = [&](int part) -> const int32_t* { return part_of(part); };
-                    if (p.epi.tma_ok)
-                        drain_tma_from<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out.m, p.n_out,
-                                                                     ParkedSource<decltype(ptr)>{ptr, p.tail_split, lane},
-                                                                     m0 + quarter * 32, lane, n0, strip, lane_s, my_stage,
-                                                                     box_count, p.epi.cols);
-                    else
-                        finish_parked<EPI, kPairNC, false>(p.epi, ptr, p.tail_split, row, n0, p.epi.cols, strip, lane_s, lane);
-                }
-            }
-#ifdef BM_TILE_TRACE
-            if (warp == 2 && lane == 0 && rank == 0) BM_TRACE(pair, trace_e, 6, global_timer_ns());
-            ++trace_e;
-#endif
+            if (p.epi.tma_ok)
+                drain_accumulator_tma<EPI, kPairNC, kPairStoreBufs>(p.epi, maps_out.m, p.n_out, taddr, row_base, lane,
+                                                                    n0, strip, lane_s, my_stage, box_count, col_limit, p.pace);
+            else
+                drain_accumulator<EPI, kPairNC, false>(p.epi, taddr, row, n0, col_limit, strip, lane_s);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
         }
         if (lane == 0) bulk_wait_all();
-#ifdef BM_TILE_TRACE
-        if (warp == 2 && lane == 0 && rank == 0) BM_TRACE(pair, 0, 7, global_timer_ns());
-#endif
     }
 
     // ---------------------------------------------------------------------- teardown

@@ -1,15 +1,24 @@
-"""N-split (column-sharded) W8A8 linear across the GPUs of one box.
+"""N-split (column-sharded) W8A8 linear layers across the GPUs of one box.
 
 The reference is single-GPU; this is the B200 form of "large GEMMs are partitioned by weight
 columns, only the output is exchanged".  Rank r owns output columns [n0, n0 + n_len) — the rows
 n0.. of W[N x K] and the matching slice of the per-channel scales — and the full activations.
 
-Two ways to assemble the output on every rank:
+Ways to assemble the output on every rank:
   * "nccl"   local GEMM, then `all_gather_into_tensor`: result laid out [world, M, n_len]
-             (rank-major column blocks); the baseline.
-  * "fused"  the GEMM epilogue itself stores each finished box of the slab into the row-major
-             [M x N] output of EVERY rank through peer-mapped symmetric memory
-             (bm_w8a8_f16_gather), followed by a group barrier; no separate gather pass.
+             (rank-major column blocks); the baseline, equal slabs only.
+  * "fused"  dense layers: the GEMM epilogue itself stores each finished box of the slab into the
+             row-major [M x N] output of EVERY rank through peer-mapped symmetric memory
+             (bm_w8a8_f16_gather; stores that cross NVLink are paced below the link rate),
+             followed by a group barrier; no separate gather pass.  Ragged slabs are fine.
+  * "push"   2:4-sparse layers: the sparse GEMM writes the slab into the rank's own [M x N]
+             output, a copy kernel (bm_gather_slab_f16) stores it to the peers, then the barrier.
+
+Output buffers of the fused / push paths are symmetric memory, two per (M, device), used in turn.
+A rank's call i+2 writes the buffer that call i returned; it is ordered behind the barrier of call
+i+1, which every rank enqueues after whatever it enqueued to read result i.  So: consume a result
+on the stream it was produced on (or order the other stream before the next call), and do not
+keep it across more than one further call of the same layer.
 
 One process per GPU (torchrun); `torch.distributed` carries the rendezvous only.
 """
@@ -41,7 +50,65 @@ def shard_weights(W_full, sw_full, world: int, rank: int, align: int = 16):
     return W_full[n0:n0 + n_len].contiguous(), sw_full[n0:n0 + n_len].contiguous(), n0, n_len
 
 
-class ColumnShardedLinear:
+def shard_sparse_weights(W_comp, W_meta_rows, sw_full, world: int, rank: int):
+    """Row slab of 2:4-compressed weights (values [N x K/2], per-row position bytes [N x K/8]) and
+    scales for `rank`.  Slabs are cut on multiples of 128 rows where N allows it (whole tiles of the
+    sparse kernel), else on multiples of 16."""
+    n_total = W_comp.shape[0]
+    align = 128 if n_total % (128 * world) == 0 else 16
+    n0, n_len = shard_columns(n_total, world, rank, align)
+    sl = slice(n0, n0 + n_len)
+    return W_comp[sl].contiguous(), W_meta_rows[sl].contiguous(), sw_full[sl].contiguous(), n0, n_len
+
+
+class _Sharded:
+    """What the dense and the sparse layer share: slab bookkeeping, symmetric output buffers, barrier."""
+
+    def __init__(self, n_total: int, n0: int, n_len: int, group, mode: str, modes: tuple):
+        if mode not in modes:
+            raise ValueError(f"mode must be one of {modes}")
+        self.n_total, self.n0, self.n_len = n_total, n0, n_len
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.mode = mode
+        self._sym = {}
+        self._turn = {}
+        lens = [None] * self.world
+        dist.all_gather_object(lens, (self.n0, self.n_len), group=self.group)
+        self.slabs = lens
+        if sum(l for _, l in lens) != n_total:
+            raise ValueError(f"column slabs {lens} do not cover N = {n_total}")
+        if mode == "nccl" and len({l for _, l in lens}) != 1:
+            raise ValueError("the NCCL all-gather path needs equal slabs; use the peer-store path for ragged splits")
+
+    def _symmetric(self, M, device):
+        """The symmetric [M x N_total] output to fill next and its handle (two per key, in turn)."""
+        key = (M, str(device))
+        if key not in self._sym:
+            import torch.distributed._symmetric_memory as symm_mem
+            pair = []
+            for _ in range(2):
+                buf = symm_mem.empty((M, self.n_total), dtype=torch.float16, device=device)
+                pair.append((buf, symm_mem.rendezvous(buf, self.group)))
+            self._sym[key] = pair
+            self._turn[key] = 0
+        turn = self._turn[key]
+        self._turn[key] = turn ^ 1
+        return self._sym[key][turn]
+
+    def _peer_slab_pointers(self, hdl):
+        col_bytes = self.n0 * 2
+        return (ctypes.c_void_p * self.world)(*[int(p) + col_bytes for p in hdl.buffer_ptrs])
+
+    @staticmethod
+    def blocks_to_row_major(blocks):
+        """[world, M, n_len] -> [M, world * n_len] (one extra pass; the peer-store paths do not need it)."""
+        w, M, n = blocks.shape
+        return blocks.permute(1, 0, 2).reshape(M, w * n)
+
+
+class ColumnShardedLinear(_Sharded):
     """D[M x N] = half(float(X W^T) * sa[m] * sw[n]) with W's rows (output columns) split over ranks.
 
     `gemm` is the local slab GEMM, (X, W_slab, D_slab_view, sa, sw_slab, M, n_len, K, ldd) -> None;
@@ -51,24 +118,10 @@ class ColumnShardedLinear:
 
     def __init__(self, W_slab, sw_slab, n_total: int, n0: int, group=None, mode: str = "nccl",
                  gemm: Optional[Callable] = None):
-        if mode not in ("nccl", "fused"):
-            raise ValueError("mode must be 'nccl' or 'fused'")
+        super().__init__(n_total, n0, W_slab.shape[0], group, mode, ("nccl", "fused"))
         self.W, self.sw = W_slab, sw_slab
-        self.n_total, self.n0, self.n_len = n_total, n0, W_slab.shape[0]
         self.K = W_slab.shape[1]
-        self.group = group if group is not None else dist.group.WORLD
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
-        self.mode = mode
         self._gemm = gemm
-        self._sym = {}
-        lens = [None] * self.world
-        dist.all_gather_object(lens, (self.n0, self.n_len), group=self.group)
-        self.slabs = lens
-        if sum(l for _, l in lens) != n_total:
-            raise ValueError(f"column slabs {lens} do not cover N = {n_total}")
-        if mode == "nccl" and len({l for _, l in lens}) != 1:
-            raise ValueError("the NCCL all-gather path needs equal slabs; use mode='fused' for ragged splits")
 
     # ---- local GEMM ------------------------------------------------------------------------
     def _local(self, X, sa, D_view, ldd):
@@ -79,48 +132,97 @@ class ColumnShardedLinear:
         from . import igemm
         igemm.w8a8_linear(X, self.W, D_view, sa, self.sw, M, self.n_len, self.K, igemm.BM_B_NK, ldd=ldd)
 
+    def forward_local(self, X, sa, out=None):
+        """The rank's slab alone, [M x n_len] (no exchange): the GEMM-only leg of a scaling measurement."""
+        M = X.shape[0]
+        if out is None:
+            out = torch.empty((M, self.n_len), dtype=torch.float16, device=X.device)
+        self._local(X, sa, out, self.n_len)
+        return out
+
     # ---- nccl baseline ---------------------------------------------------------------------
     def forward_nccl(self, X, sa, out=None, local=None):
         """Returns [world, M, n_len] (rank-major column blocks)."""
         M = X.shape[0]
-        if local is None:
-            local = torch.empty((M, self.n_len), dtype=torch.float16, device=X.device)
-        self._local(X, sa, local, self.n_len)
+        local = self.forward_local(X, sa, local)
         if out is None:
             out = torch.empty((self.world, M, self.n_len), dtype=torch.float16, device=X.device)
         dist.all_gather_into_tensor(out.view(self.world * M, self.n_len), local, group=self.group)
         return out
 
-    @staticmethod
-    def blocks_to_row_major(blocks):
-        """[world, M, n_len] -> [M, world * n_len] (one extra pass; the fused path does not need it)."""
-        w, M, n = blocks.shape
-        return blocks.permute(1, 0, 2).reshape(M, w * n)
-
     # ---- fused GEMM + gather ---------------------------------------------------------------
-    def _symmetric(self, M, device):
-        key = (M, str(device))
-        if key not in self._sym:
-            import torch.distributed._symmetric_memory as symm_mem
-            buf = symm_mem.empty((M, self.n_total), dtype=torch.float16, device=device)
-            hdl = symm_mem.rendezvous(buf, self.group)
-            self._sym[key] = (buf, hdl)
-        return self._sym[key]
-
-    def forward_fused(self, X, sa):
-        """Returns this rank's row-major [M x N] output, complete once the trailing barrier has run."""
+    def forward_fused(self, X, sa, barrier: bool = True):
+        """Returns this rank's row-major [M x N] output, complete once the trailing barrier has run
+        (see the module text for how long it stays valid)."""
         from . import _lib, igemm
         M = X.shape[0]
         buf, hdl = self._symmetric(M, X.device)
-        col_bytes = self.n0 * 2
-        ptrs = (ctypes.c_void_p * self.world)(*[int(p) + col_bytes for p in hdl.buffer_ptrs])
+        ptrs = self._peer_slab_pointers(hdl)
         L = _lib.load()
-        rc = L.bm_w8a8_f16_gather(X.data_ptr(), self.W.data_ptr(), ptrs, self.world, sa.data_ptr(), self.sw.data_ptr(),
-                                  M, self.n_len, self.K, self.n_total, igemm.BM_B_NK,
+        rc = L.bm_w8a8_f16_gather(X.data_ptr(), self.W.data_ptr(), ptrs, self.world, self.rank, sa.data_ptr(),
+                                  self.sw.data_ptr(), M, self.n_len, self.K, self.n_total, igemm.BM_B_NK,
                                   torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "bm_w8a8_f16_gather")
-        hdl.barrier()            # every rank's stores have been issued and completed before anyone reads
+        if barrier:
+            hdl.barrier()        # every rank's stores have been issued and completed before anyone reads
         return buf
 
     def forward(self, X, sa):
         return self.forward_fused(X, sa) if self.mode == "fused" else self.forward_nccl(X, sa)
+
+
+class ColumnShardedSparseLinear(_Sharded):
+    """The same layer with 2:4-sparse weights: rank r holds rows [n0, n0 + n_len) of the compressed
+    weights W_comp[N x K/2], their position metadata in the kernel's tiled order (bm_sp_pack_meta of
+    the slab) and the scales.  Decode shapes (a few tokens) and prefill shapes both go through
+    bm_w8a8_sparse_f16, which picks its kernel by the token count.
+
+    `gemm` as for the dense layer: (X, W_comp_slab, meta_slab, D_slab_view, sa, sw_slab, M, n_len, K, ldd).
+    """
+
+    def __init__(self, W_comp_slab, W_meta_tiled_slab, sw_slab, n_total: int, n0: int, group=None,
+                 mode: str = "push", gemm: Optional[Callable] = None):
+        super().__init__(n_total, n0, W_comp_slab.shape[0], group, mode, ("nccl", "push"))
+        self.W_comp, self.W_meta, self.sw = W_comp_slab, W_meta_tiled_slab, sw_slab
+        self.K = W_comp_slab.shape[1] * 2
+        self._gemm = gemm
+
+    def _local(self, X, sa, D_view, ldd):
+        M = X.shape[0]
+        if self._gemm is not None:
+            self._gemm(X, self.W_comp, self.W_meta, D_view, sa, self.sw, M, self.n_len, self.K, ldd)
+            return
+        from . import igemm
+        igemm.w8a8_sparse_linear(X, self.W_comp, self.W_meta, D_view, sa, self.sw, M, self.n_len, self.K, ldd=ldd)
+
+    def forward_local(self, X, sa, out=None):
+        M = X.shape[0]
+        if out is None:
+            out = torch.empty((M, self.n_len), dtype=torch.float16, device=X.device)
+        self._local(X, sa, out, self.n_len)
+        return out
+
+    def forward_nccl(self, X, sa, out=None, local=None):
+        M = X.shape[0]
+        local = self.forward_local(X, sa, local)
+        if out is None:
+            out = torch.empty((self.world, M, self.n_len), dtype=torch.float16, device=X.device)
+        dist.all_gather_into_tensor(out.view(self.world * M, self.n_len), local, group=self.group)
+        return out
+
+    def forward_push(self, X, sa, barrier: bool = True):
+        """Local sparse GEMM into the rank's own [M x N] output, peer stores of the slab, barrier."""
+        from . import _lib
+        M = X.shape[0]
+        buf, hdl = self._symmetric(M, X.device)
+        self._local(X, sa, buf[:, self.n0:self.n0 + self.n_len], self.n_total)
+        ptrs = self._peer_slab_pointers(hdl)
+        rc = _lib.load().bm_gather_slab_f16(ptrs, self.world, self.rank, M, self.n_len, self.n_total,
+                                            torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "bm_gather_slab_f16")
+        if barrier:
+            hdl.barrier()
+        return buf
+
+    def forward(self, X, sa):
+        return self.forward_push(X, sa) if self.mode == "push" else self.forward_nccl(X, sa)

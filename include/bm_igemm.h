@@ -79,11 +79,24 @@ int bm_w8a8_f16(const int8_t *X, const int8_t *W, uint16_t *D, const float *sa_m
  * and the epilogue stores every finished box to the `n_peers` (<= 8) destinations in `D_peers`:
  * HOST array of DEVICE pointers, each already pointing at the slab's first column inside that
  * GPU's [M x N_total] output (peer-mapped memory for the other GPUs, e.g. symmetric memory).
- * `ldd` = N_total.  Plain TMA stores, no multicast.  The caller orders the kernel against its peers
- * (a barrier across the group after the launch) before anyone reads D. */
+ * `self_index` names the entry that is this GPU's own buffer (-1: none — every destination is
+ * treated as remote).  Stores to the other entries cross NVLink and are paced to the rate of
+ * option "gather_gbs" (GB/s this GPU may send; 0 = unpaced): peer stores offered faster than the
+ * link drains them stall the operand loads of the whole GPU.  `ldd` = N_total.  Plain TMA stores,
+ * no multicast.  The caller orders the kernel against its peers (a barrier across the group after
+ * the launch) before anyone reads D. */
 int bm_w8a8_f16_gather(const int8_t *X, const int8_t *W, uint16_t *const *D_peers, int n_peers,
-                       const float *sa_m, const float *sw_n, int M, int N, int K, int64_t ldd,
-                       int w_layout, void *stream);
+                       int self_index, const float *sa_m, const float *sw_n, int M, int N, int K,
+                       int64_t ldd, int w_layout, void *stream);
+
+/* All-gather of an fp16 column slab by plain peer stores (no reference counterpart), for N-split
+ * layers whose GEMM does not gather by itself (the 2:4-sparse entry points).  The rank's slab
+ * [M x n_len] already sits in its own [M x N_total] output at D_peers[self_index]; it is copied to
+ * the same place in the other `n_peers - 1` outputs (peer-mapped pointers).  Local 16-byte loads,
+ * paced 16-byte peer stores ("gather_gbs"); no peer loads, no multicast.  n_len % 8 == 0,
+ * ldd % 8 == 0.  The caller orders it against its peers (group barrier) before anyone reads. */
+int bm_gather_slab_f16(uint16_t *const *D_peers, int n_peers, int self_index, int M, int n_len,
+                       int64_t ldd, void *stream);
 
 /* Per-token dynamic quantisation fp16 -> int8, the step before the W8A8 GEMM.  B200 form of the
  * reference's online-quant kernels (igemm_online_quant.cu:144-150 take fp16 and quantise per K tile
@@ -166,14 +179,31 @@ int bm_igemm_sparse_f32(const int8_t *A_comp, const int8_t *B, float *C, const u
 /* No counterpart in the reference.  Same arguments and result as bm_igemm_sparse_f32, for callers
  * that must not allocate device memory (a serving loop with a fixed memory footprint, a process
  * whose pool owns the whole device, start-up-only allocation policies): the re-tiled metadata
- * lives in a fixed 2 MiB array inside the library instead of cudaMalloc'ed scratch, and no CUDA
- * allocation or free is ever made.  Limits: ceil(M/128) * ceil(K/256) * 4096 bytes <= 2 MiB
+ * lives in a fixed 2 MiB array inside the library instead of cudaMalloc'ed scratch, and the call
+ * makes no CUDA allocation or free.  Limits: ceil(M/128) * ceil(K/256) * 4096 bytes <= 2 MiB
  * (M = K = 4096 fits), otherwise BM_ERR_TOO_LARGE and nothing is launched; N % 16 == 0.  All
  * calls on a device share the array: calls that overlap on the GPU race, so keep them on one
- * stream or order them.  The first call on each device resolves the array's device address;
- * make it with that device current and outside stream capture. */
+ * stream or order them.
+ * First call on a device: it resolves the array's device address, and — under the CUDA runtime's
+ * default lazy module loading — it is also the moment the runtime loads this library's device
+ * image there, which reserves the 2 MiB array and the kernel code.  Make that call with the device
+ * current, outside stream capture, and BEFORE a pool claims the rest of the device's memory (or
+ * run with CUDA_MODULE_LOADING=EAGER, which moves the reservation to context creation).
+ * A bounded wait that gives up inside one of its launches is recorded in a status word of its
+ * own: read it with bm_noalloc_last_device_status. */
 int bm_igemm_sparse_f32_noalloc(const int8_t *A_comp, const int8_t *B, float *C, const uint32_t *meta,
                                 int M, int N, int K, float scale_a, float scale_b, void *stream);
+/* No counterpart in the reference.  Reads (and clears) the status word of the no-alloc entry
+ * point on the current device without allocating anything: *code 0 = no launch gave up, or the
+ * entry point has not been used on this device.  Synchronises the device.
+ * bm_last_device_status reports the same word, but its first use creates the library's regular
+ * per-device state with a 4-byte cudaMalloc — callers that may not allocate use this one. */
+int bm_noalloc_last_device_status(int *code);
+/* Failure-detection self-test of that status channel (no allocation): a one-CTA kernel waits, with
+ * a limit of `limit_us`, on a barrier nothing signals and records the give-up in the no-alloc
+ * status word.  *outcome = 2 when the wait gave up cleanly; bm_noalloc_last_device_status then
+ * returns code 5 once.  The device context stays usable. */
+int bm_noalloc_selftest_bounded_wait(unsigned limit_us, int *outcome);
 
 /* Sparse-left, int32 out, any metadata format, either layout of the dense operand. */
 int bm_igemm_sparse_i32(const int8_t *A_comp, const void *meta, int meta_format, const int8_t *B,
@@ -203,8 +233,22 @@ int bm_w8a8_sparse_f16_packed(const int8_t *X, const void *W_packed, uint16_t *D
  * Library state
  * ===================================================================================== */
 /* Reads (and clears) the device status word that a bounded in-kernel wait sets when it gives
- * up: *code 0 = none.  Synchronises the device. */
+ * up: *code 0 = none.  Synchronises the whole device (every stream), so call it at checkpoints,
+ * not per launch.  Also reports a give-up recorded by the no-alloc entry point. */
 int bm_last_device_status(int *code);
+/* Launcher options (tuning / testing switches; no reference counterpart — the reference fixes
+ * launch geometry in its bench drivers, bench.cu:375-636).  Names: "force_bn" (pin the tile width;
+ * 0 = choose), "dense_pair", "sparse_pair" (0 = single-CTA kernels only), "row_balanced",
+ * "stream_k" (-1 automatic, 0 never, 1 wherever possible), "tma_store" (0 = direct-store
+ * epilogue), "dense_group_m", "sparse_col_first" (-1 automatic), "tail_narrow", "pdl", "gather_gbs".
+ * Each starts from the environment variable BM_<NAME> read once at first use, else its default;
+ * launchers never read the environment on the launch path.  Process-wide; set them while no
+ * other thread is launching.  Unknown names return BM_ERR_LAYOUT. */
+int bm_set_option(const char *name, int value);
+int bm_get_option(const char *name, int *value);
+/* TMA descriptors are cached by (address, shape, pitch, box): counts of lookups served from the
+ * cache, descriptors encoded, and entries held.  Any pointer may be NULL. */
+int bm_tensor_map_cache_stats(uint64_t *hits, uint64_t *misses, uint64_t *entries);
 /* Failure-detection self-test (no reference counterpart; the reference's persistent kernels have
  * no watchdog): runs a one-CTA kernel that waits, with a limit of `limit_us`, on a barrier nothing
  * signals.  *outcome = 2 when the wait gave up cleanly; bm_last_device_status then reports the
@@ -212,7 +256,8 @@ int bm_last_device_status(int *code);
 int bm_selftest_bounded_wait(unsigned limit_us, int *outcome);
 /* Text of the last host-side CUDA error seen by a launcher on this thread. */
 const char *bm_last_error_string(void);
-/* Frees library-owned scratch (metadata staging, status word). */
+/* Frees library-owned scratch (metadata staging, split-K partial sums, status word) and empties
+ * the descriptor cache. */
 void bm_shutdown(void);
 /* "major.minor" of this ABI. */
 const char *bm_version(void);

@@ -15,20 +15,22 @@ def T(a):
 
 
 @contextmanager
-def forced_bn(bn):
-    """Pin the tile width (launcher testing hook) for the duration of the block."""
-    old = os.environ.get("BM_FORCE_BN")
-    if bn is None:
-        os.environ.pop("BM_FORCE_BN", None)
-    else:
-        os.environ["BM_FORCE_BN"] = str(bn)
+def options(**kv):
+    """Temporarily set launcher options (bm_set_option) for the duration of the block."""
+    from bare_metal_b200 import _lib
+    old = {k: _lib.get_option(k) for k in kv}
+    for k, v in kv.items():
+        _lib.set_option(k, v)
     try:
         yield
     finally:
-        if old is None:
-            os.environ.pop("BM_FORCE_BN", None)
-        else:
-            os.environ["BM_FORCE_BN"] = old
+        for k, v in old.items():
+            _lib.set_option(k, v)
+
+
+def forced_bn(bn):
+    """Pin the tile width (launcher testing hook) for the duration of the block."""
+    return options(force_bn=0 if bn is None else bn)
 
 
 def ulp_diff_f16(a_bits: np.ndarray, b_bits: np.ndarray) -> int:
@@ -43,25 +45,6 @@ def assert_clean_status():
     from bare_metal_b200 import igemm
     torch.cuda.synchronize()
     assert igemm.last_device_status() == 0, "a bounded device-side wait gave up"
-
-
-@contextmanager
-def env(**kv):
-    """Temporarily set environment variables read by the launchers' testing hooks."""
-    old = {k: os.environ.get(k) for k in kv}
-    for k, v in kv.items():
-        if v is None:
-            os.environ.pop(k, None)
-        else:
-            os.environ[k] = str(v)
-    try:
-        yield
-    finally:
-        for k, v in old.items():
-            if v is None:
-                os.environ.pop(k, None)
-            else:
-                os.environ[k] = v
 
 
 class RefKernel:

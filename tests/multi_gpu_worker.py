@@ -1,5 +1,6 @@
-"""Worker run under torchrun by test_gpu_multi.py: N-split linear on real GPUs, both gather paths,
-checked against the CPU oracle on every rank.  Exit code 0 = all checks passed on this rank."""
+"""Worker run under torchrun by test_gpu_multi.py (and by hand on 2 / 4 / 8 GPUs): the N-split layers on
+real GPUs, every gather path, checked against the CPU oracle on every rank.  Exit code 0 = all checks
+passed on this rank.  `--full` adds the full-size shapes of the 8192-token layer (sampled rows)."""
 import os
 import sys
 
@@ -10,7 +11,64 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 import oracle  # noqa: E402
+from bare_metal_b200 import igemm as ig  # noqa: E402
 from bare_metal_b200 import nsplit  # noqa: E402
+
+
+def check_dense(dev, rank, world, M, N, K, seed, rows=None, nccl=True):
+    """Both gather paths of the dense layer; with `rows`, only those output rows are compared (full-size shapes)."""
+    W = oracle.gen_int8((N, K), seed, 2)
+    sw = oracle.gen_scales(N, seed, 4)
+    Wt, swt = torch.from_numpy(W).to(dev), torch.from_numpy(sw).to(dev)
+    W_slab, sw_slab, n0, n_len = nsplit.shard_weights(Wt, swt, world, rank)
+    del Wt
+    fused = nsplit.ColumnShardedLinear(W_slab, sw_slab, N, n0, mode="fused")
+    equal = len({l for _, l in fused.slabs}) == 1
+    base = nsplit.ColumnShardedLinear(W_slab, sw_slab, N, n0, mode="nccl") if (nccl and equal) else None
+    for it in range(3):                      # different activations every time: a stale or early peer write would show
+        X = oracle.gen_int8((M, K), seed + it, 1)
+        sa = oracle.gen_scales(M, seed + it, 3)
+        sel = np.arange(M) if rows is None else rows
+        want = oracle.dequant_w8a8_f16(oracle.igemm_nt(np.ascontiguousarray(X[sel]), W), sa[sel], sw).view(np.uint16)
+        Xd, sad = torch.from_numpy(X).to(dev), torch.from_numpy(sa).to(dev)
+        full = fused.forward(Xd, sad)
+        torch.cuda.synchronize()
+        got = full.cpu().numpy().view(np.uint16)[sel]
+        assert np.array_equal(got, want), f"rank {rank}: fused gather differs from the oracle ({M}x{N}x{K}, pass {it})"
+        if base is not None and it == 0:
+            blocks = base.forward(Xd, sad)
+            torch.cuda.synchronize()
+            got = nsplit.ColumnShardedLinear.blocks_to_row_major(blocks).cpu().numpy().view(np.uint16)[sel]
+            assert np.array_equal(got, want), f"rank {rank}: NCCL gather path differs from the oracle ({M}x{N}x{K})"
+    assert ig.last_device_status() == 0, "a bounded device-side wait gave up"
+
+
+def check_sparse(dev, rank, world, M, N, K, seed, rows=None):
+    """2:4-sparse weights, N-split: local sparse GEMM + peer-store gather (and the NCCL path for equal slabs)."""
+    comp, nib = oracle.gen_sparse_rows(N, K, seed, 5)
+    sw = oracle.gen_scales(N, seed, 4)
+    Wdense = oracle.decompress_rows(comp, nib)
+    c_slab, m_slab, sw_slab, n0, n_len = nsplit.shard_sparse_weights(
+        torch.from_numpy(comp).to(dev), torch.from_numpy(nib).to(dev), torch.from_numpy(sw).to(dev), world, rank)
+    tiled = ig.sp_pack_meta(m_slab, ig.BM_META_ROWS, n_len, K)
+    push = nsplit.ColumnShardedSparseLinear(c_slab, tiled, sw_slab, N, n0, mode="push")
+    equal = len({l for _, l in push.slabs}) == 1
+    for it in range(3):
+        X = oracle.gen_int8((M, K), seed + it, 1)
+        sa = oracle.gen_scales(M, seed + it, 3)
+        sel = np.arange(M) if rows is None else rows
+        want = oracle.dequant_w8a8_f16(oracle.igemm_nt(np.ascontiguousarray(X[sel]), Wdense), sa[sel], sw).view(np.uint16)
+        Xd, sad = torch.from_numpy(X).to(dev), torch.from_numpy(sa).to(dev)
+        full = push.forward(Xd, sad)
+        torch.cuda.synchronize()
+        got = full.cpu().numpy().view(np.uint16)[sel]
+        assert np.array_equal(got, want), f"rank {rank}: sparse push gather differs from the oracle ({M}x{N}x{K}, pass {it})"
+        if equal and it == 0:
+            blocks = nsplit.ColumnShardedSparseLinear(c_slab, tiled, sw_slab, N, n0, mode="nccl").forward(Xd, sad)
+            torch.cuda.synchronize()
+            got = nsplit.ColumnShardedLinear.blocks_to_row_major(blocks).cpu().numpy().view(np.uint16)[sel]
+            assert np.array_equal(got, want), f"rank {rank}: sparse NCCL gather differs from the oracle ({M}x{N}x{K})"
+    assert ig.last_device_status() == 0, "a bounded device-side wait gave up"
 
 
 def main():
@@ -19,26 +77,26 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
+    full = "--full" in sys.argv
     try:
-        for (M, N, K) in ((512, 1024 * world, 1024), (300, 256 * world, 512)):
-            X = oracle.gen_int8((M, K), 0, 1)
-            W = oracle.gen_int8((N, K), 0, 2)
-            sa, sw = oracle.gen_scales(M, 0, 3), oracle.gen_scales(N, 0, 4)
-            want = oracle.dequant_w8a8_f16(oracle.igemm_nt(X, W), sa, sw).view(np.uint16)
-            Wt, swt = torch.from_numpy(W).to(dev), torch.from_numpy(sw).to(dev)
-            W_slab, sw_slab, n0, n_len = nsplit.shard_weights(Wt, swt, world, rank)
-            Xd, sad = torch.from_numpy(X).to(dev), torch.from_numpy(sa).to(dev)
-            base = nsplit.ColumnShardedLinear(W_slab, sw_slab, N, n0, mode="nccl")
-            blocks = base.forward(Xd, sad)
-            torch.cuda.synchronize()
-            got = nsplit.ColumnShardedLinear.blocks_to_row_major(blocks).cpu().numpy().view(np.uint16)
-            assert np.array_equal(got, want), f"rank {rank}: NCCL gather path differs from the oracle"
-            fused = nsplit.ColumnShardedLinear(W_slab, sw_slab, N, n0, mode="fused")
-            for _ in range(2):                     # twice: buffers and barrier are reused
-                full = fused.forward(Xd, sad)
-                torch.cuda.synchronize()
-                got = full.cpu().numpy().view(np.uint16)
-                assert np.array_equal(got, want), f"rank {rank}: fused gather differs from the oracle"
+        # equal slabs, multiples of 128; then a tall ragged-M case
+        check_dense(dev, rank, world, 512, 1024 * world, 1024, 0)
+        check_dense(dev, rank, world, 300, 256 * world, 512, 10)
+        # ragged split in the proportions of the gate+up projection (22016 columns over 8 GPUs = 2752 each,
+        # not a multiple of 128): 344 columns per rank on average, slabs of 336 / 352
+        check_dense(dev, rank, world, 777, 344 * world, 640, 20)
+        # enough tiles for several waves of CTA pairs and a partly filled last one
+        check_dense(dev, rank, world, 2304, 2560 * world, 256, 30)
+        # 2:4-sparse layers: decode shapes (1 and 64 tokens; 3584 channels per rank at full size) and a prefill chunk
+        check_sparse(dev, rank, world, 1, 448 * world, 1024, 40)
+        check_sparse(dev, rank, world, 64, 448 * world, 2048, 50)
+        check_sparse(dev, rank, world, 300, 280 * world, 512, 60)
+        if full:
+            rows = np.array([0, 1, 127, 128, 4095, 4096, 8191])
+            # the 8192-token layer's largest projection, split as the workload says (2752 columns per rank at 8)
+            check_dense(dev, rank, world, 8192, 22016, 4096, 70, rows=rows, nccl=False)
+            check_dense(dev, rank, world, 4096, 4096, 4096, 80, rows=rows[:5], nccl=False)
+            check_sparse(dev, rank, world, 64, 28672, 8192, 90, rows=np.array([0, 1, 31, 63]))
         dist.barrier()
         print(f"rank {rank}: ok", flush=True)
     finally:

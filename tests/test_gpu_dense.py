@@ -170,54 +170,20 @@ def test_bad_arguments_raise_on_the_gpu_too():
         ig.igemm_i32(a, a, c.float(), 128, 128, 32, ig.BM_B_NK)     # wrong output dtype
 
 
-@pytest.mark.parametrize("M,N,K,layout", [(2560, 2304, 512, ig.BM_B_NK), (2500, 2320, 272, ig.BM_B_KN),
-                                          (2816, 2048, 1024, ig.BM_B_NK)])
-def test_tail_split_of_the_last_wave(M, N, K, layout):
-    """More 256x256 tiles than CTA pairs with a partly filled last wave: its tiles are cut into K
-    ranges for different pairs and the partial sums are added exactly (int32), then dequantised once.
-    Run twice so the self-resetting arrival counters are exercised."""
-    A = oracle.gen_int8((M, K), 11, 1)
-    B = oracle.gen_int8((K, N), 11, 2)
-    acc = oracle.igemm(A, B, threads=0)
-    sa, sw = oracle.gen_scales(M, 11, 3), oracle.gen_scales(N, 11, 4)
-    want16 = oracle.dequant_w8a8_f16(acc, sa, sw).view(np.uint16)
-    Bd = T(B) if layout == ig.BM_B_KN else T(B.T)
-    from _gpu import env
-    with env(BM_TAIL_SPLIT=2):
-        for _ in range(2):
-            C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
-            ig.igemm_i32(T(A), Bd, C, M, N, K, layout)
-            assert_clean_status()
-            assert np.array_equal(C.cpu().numpy(), acc)
-            D = torch.zeros((M, N), dtype=torch.float16, device=dev())
-            ig.w8a8_linear(T(A), Bd, D, T(sa), T(sw), M, N, K, layout)
-            assert_clean_status()
-            assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
-        # through the unaligned (direct-store) path
-        wide = torch.zeros((M, N + 1), dtype=torch.int32, device=dev())
-        ig.igemm_i32(T(A), Bd, wide[:, :N], M, N, K, layout)
-        assert_clean_status()
-        assert np.array_equal(wide.cpu().numpy()[:, :N], acc)
-    # same integers with the split off (the default)
-    C2 = torch.empty((M, N), dtype=torch.int32, device=dev())
-    ig.igemm_i32(T(A), Bd, C2, M, N, K, layout)
-    assert np.array_equal(C2.cpu().numpy(), acc)
-
-
 @pytest.mark.parametrize("M,N,K", [(2560, 2304, 512), (2500, 2256, 272), (2500, 2250, 144), (2816, 2048, 1024)])
 def test_half_height_tiles_in_the_last_wave(M, N, K):
     """More 256x256 tiles than CTA pairs and a last wave at most half full: its tiles are computed as two
     128x256 halves by different pairs (M = 128 pair MMAs, 64 rows per CTA).  Same integers as with the
     half-height tail off, for every epilogue and both weight layouts, ragged edges included; canary rows
     catch stores outside the output."""
-    from _gpu import env
+    from _gpu import options
     A = oracle.gen_int8((M, K), 12, 1)
     B = oracle.gen_int8((K, N), 12, 2)
     acc = oracle.igemm(A, B, threads=0)
     assert np.array_equal(run_i32(A, B, ig.BM_B_NK, guard=True), acc)
     if N % 16 == 0:
         assert np.array_equal(run_i32(A, B, ig.BM_B_KN, guard=True), acc)
-    with env(BM_TAIL_NARROW=0):
+    with options(tail_narrow=0):
         assert np.array_equal(run_i32(A, B, ig.BM_B_NK, guard=True), acc)
     Bd = T(B.T)
     sa, sw = oracle.gen_scales(M, 12, 3), oracle.gen_scales(N, 12, 4)
@@ -237,11 +203,11 @@ def test_half_height_tiles_in_the_last_wave(M, N, K):
 def test_banded_tile_order_gives_the_same_integers(group):
     """Tile order of the pair kernel (plain, or bands of G row tiles — chosen for tall problems): the
     integers do not depend on it; 21 row tiles make the last band short for G = 8."""
-    from _gpu import env
+    from _gpu import options
     M, N, K = 5300, 1000, 256
     A = oracle.gen_int8((M, K), 13, 1)
     B = oracle.gen_int8((K, N), 13, 2)
-    with env(BM_DENSE_GROUP_M=group), forced_bn(256):
+    with options(dense_group_m=group), forced_bn(256):
         got = run_i32(A, B, ig.BM_B_NK, guard=True)
     assert np.array_equal(got, oracle.igemm(A, B, threads=0))
 

@@ -1,5 +1,6 @@
-"""N-split linear on 2 real GPUs (skipped on a single-GPU box): NCCL all-gather baseline and the
-gather fused into the GEMM epilogue (peer TMA stores), both against the CPU oracle."""
+"""N-split layers on 2 real GPUs (skipped on a single-GPU box): the NCCL all-gather baseline, the gather
+fused into the dense GEMM's epilogue (paced peer TMA stores) on equal and ragged slabs, and the 2:4-sparse
+layers with their peer-store gather, all against the CPU oracle."""
 import os
 import socket
 import subprocess

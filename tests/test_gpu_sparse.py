@@ -175,14 +175,14 @@ def test_packed_sparse_weights_match_oracle(M, N, K, bn):
 def test_stream_k_split_matches_oracle(M, N, K, bn):
     """K ranges of a tile shared between CTAs (stream-K): partial sums are added exactly, whatever
     the split; run twice so the self-resetting arrival counters are exercised."""
-    from _gpu import env
+    from _gpu import options
     comp, nib = oracle.gen_sparse_rows(N, K, 3, 41)
     X = oracle.gen_int8((M, K), 3, 42)
     want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
     packed = ig.sp_pack_weights(T(comp), T(nib), ig.BM_META_ROWS, N, K)
     sa, sw = oracle.gen_scales(M, 3, 3), oracle.gen_scales(N, 3, 4)
     want16 = oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)
-    with env(BM_STREAM_K=1), forced_bn(bn):
+    with options(stream_k=1), forced_bn(bn):
         for _ in range(2):
             C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
             ig.w8a8_sparse_i32_packed(T(X), packed, C, M, N, K)
@@ -193,18 +193,18 @@ def test_stream_k_split_matches_oracle(M, N, K, bn):
             assert_clean_status()
             assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
     # the static schedule gives the same integers
-    with env(BM_STREAM_K=0), forced_bn(bn):
+    with options(stream_k=0), forced_bn(bn):
         C2 = torch.empty((M, N), dtype=torch.int32, device=dev())
         ig.w8a8_sparse_i32_packed(T(X), packed, C2, M, N, K)
         assert np.array_equal(C2.cpu().numpy(), want)
 
 
 def test_stream_k_reference_left_orientation():
-    from _gpu import env
+    from _gpu import options
     M, N, K = 384, 256, 2048
     dense, comp, meta, B = bench_sparse_inputs(M, N, K)
     want = oracle.igemm(dense, B, threads=0)
-    with env(BM_STREAM_K=1):
+    with options(stream_k=1):
         C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
         ig.igemm_sparse_i32(T(comp), T(meta.view(np.int32)), ig.BM_META_REF, T(B), C, M, N, K, ig.BM_B_KN)
         assert_clean_status()
@@ -237,7 +237,7 @@ def test_sparse_weights_on_cta_pairs(M, N, K):
 def test_row_balanced_decode_tiles(M, N, K):
     """Decode shapes on packed weights: rows are dealt to the SMs in multiples of 8 (ragged last
     tiles fetch only their own rows); results must not depend on where the cuts fall."""
-    from _gpu import env
+    from _gpu import options
     comp, nib = oracle.gen_sparse_rows(N, K, 5, 61)
     X = oracle.gen_int8((M, K), 5, 62)
     want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
@@ -245,7 +245,7 @@ def test_row_balanced_decode_tiles(M, N, K):
     sa, sw = oracle.gen_scales(M, 5, 3), oracle.gen_scales(N, 5, 4)
     want16 = oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)
     for balanced in (1, 0):
-        with env(BM_ROW_BALANCED=balanced):
+        with options(row_balanced=balanced, stream_k=0):
             guard = torch.full((M + 2, N), 0x5A5A5A5A, dtype=torch.int32, device=dev())
             ig.w8a8_sparse_i32_packed(T(X), packed, guard[1:M + 1], M, N, K)
             assert_clean_status()
@@ -305,13 +305,13 @@ def test_reference_orientation_on_cta_pairs(M, N, K):
 def test_pair_kernel_tile_orders_give_the_same_integers(order):
     """Sparse weights on CTA pairs with row blocks fastest and with column tiles fastest (the order picked
     for weights larger than L2): exact int32 either way, ragged tiles on both axes."""
-    from _gpu import env
+    from _gpu import options
     M, N, K = 500, 1100, 512                      # 3 token tiles of 240, 5 channel blocks of 256
     comp, nib = oracle.gen_sparse_rows(N, K, 31, 1)
     X = oracle.gen_int8((M, K), 31, 2)
     tiled = ig.sp_pack_meta(T(nib), ig.BM_META_ROWS, N, K)
     C = torch.full((M, N), -9, dtype=torch.int32, device=dev())
-    with env(BM_SPARSE_COL_FIRST=order), forced_bn(240):
+    with options(sparse_col_first=order), forced_bn(240):
         ig.w8a8_sparse_i32(T(X), T(comp), tiled, C, M, N, K)
     assert_clean_status()
     assert np.array_equal(C.cpu().numpy(), oracle.igemm_nt(X, oracle.decompress_rows(comp, nib)))
