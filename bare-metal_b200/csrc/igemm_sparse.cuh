@@ -161,6 +161,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
     using Cfg = SparseCfg<BN>;
     static_assert(!DENSE_MN || BN % 128 == 0, "MN-major dense operand is loaded in 128-column boxes");
     static_assert(!F16 || (DENSE_MN && !TRANSPOSED && !PACKED && EPI == EPI_I32), "fp16: reference orientation only");
+    constexpr bool ROTATE_K = TRANSPOSED && BN <= 64;         // decode shapes: per-CTA starting K block (see the producer)
     constexpr int kKRows = F16 ? 128 : kSpKLogical;          // logical K (= rows of B[K x N]) per stage
     constexpr int kMetaStage = F16 ? 2048 : kSpMetaBytes;    // metadata bytes fetched per stage
     extern __shared__ uint8_t smem_raw[];
@@ -229,7 +230,13 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                 const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) *
                                                              (F16 ? (p.k_blocks + 1) / 2 : p.k_blocks) *
                                                              (PACKED ? kSpPackedBlock : kSpMetaBytes);
-                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+                // Decode shapes: every CTA walks the K blocks of its tile from a different starting block and wraps
+                // around (exact integer sums do not care about the order).  All CTAs read the SAME few tokens; in
+                // lockstep they would all ask the L2 for the same 16 KiB of activations at the same moment.
+                const bool whole_k = seg.kb0 == 0 && seg.kb1 == p.k_blocks;
+                const int rot = (ROTATE_K && whole_k) ? static_cast<int>((blockIdx.x * 7u) % static_cast<unsigned>(p.k_blocks)) : 0;
+                for (int kb_seq = seg.kb0; kb_seq < seg.kb1; ++kb_seq) {
+                    const int kb = kb_seq + rot < p.k_blocks ? kb_seq + rot : kb_seq + rot - p.k_blocks;
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
                     const uint32_t bar = full_bar(stage);

@@ -226,3 +226,31 @@ class ColumnShardedSparseLinear(_Sharded):
 
     def forward(self, X, sa):
         return self.forward_push(X, sa) if self.mode == "push" else self.forward_nccl(X, sa)
+
+
+def measure_peer_store_bandwidth(device, group=None, rows: int = 8192, cols_per_rank: int = 1024, timeit=None) -> float:
+    """GB/s a rank receives while every rank of the group pushes an fp16 slab of `rows x cols_per_rank` to all the
+    others at the same time with the library's copy kernel (bm_gather_slab_f16), pacing switched off: what plain
+    peer stores achieve on this box, in this run.  Collective: call it on every rank.  `timeit(fn)` must return
+    the milliseconds one call of fn(i) takes, measured on the device across the group."""
+    from . import _lib
+    group = group if group is not None else dist.group.WORLD
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if world < 2:
+        raise ValueError("needs at least two ranks")
+    n_total = cols_per_rank * world
+    probe = _Sharded(n_total, rank * cols_per_rank, cols_per_rank, group, "push", ("push",))
+    buf, hdl = probe._symmetric(rows, device)
+    ptrs = probe._peer_slab_pointers(hdl)
+    L = _lib.load()
+    old = _lib.get_option("gather_gbs")
+    _lib.set_option("gather_gbs", 0)
+    try:
+        def push(i):
+            _lib.check(L.bm_gather_slab_f16(ptrs, world, rank, rows, cols_per_rank, n_total,
+                                            torch.cuda.current_stream().cuda_stream), "bm_gather_slab_f16")
+        ms = timeit(push)
+    finally:
+        _lib.set_option("gather_gbs", old)
+    hdl.barrier()
+    return 2.0 * rows * cols_per_rank * (world - 1) / (ms * 1e-3) / 1e9

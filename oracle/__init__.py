@@ -28,6 +28,16 @@ _sz = C.c_size_t
 _u64 = C.c_uint64
 
 
+def reference_root():
+    """Checkout of the reference project: $BM_REFERENCE_ROOT, else a directory `reference` beside this
+    repository; None when there is none (the prebuilt files under oracle/_ref are then used as they are)."""
+    env = os.environ.get("BM_REFERENCE_ROOT")
+    if env:
+        return env if os.path.isdir(env) else None
+    beside = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return beside if os.path.isdir(os.path.join(beside, "kernels", "gemm", "igemm")) else None
+
+
 def build(force: bool = False) -> None:
     """Compile the checker (and the in-place reference build when the reference
     checkout is present).  Building the checker is not using it."""
@@ -35,14 +45,18 @@ def build(force: bool = False) -> None:
         os.path.getmtime(_ORC_PATH) < os.path.getmtime(os.path.join(_HERE, "igemm_oracle.c")))
     if stale:
         subprocess.run(["make", "-C", _HERE, "liborc.so"], check=True, capture_output=True)
-    ref_root = os.environ.get("BM_REFERENCE_ROOT", "/root/reference")
+    ref_root = reference_root()
+    if ref_root is None:
+        return
     if os.path.isdir(ref_root) and (force or not os.path.exists(_REF_PATH)):
         subprocess.run(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root}"], check=True,
                        capture_output=True)
     if os.path.isdir(ref_root) and (force or not os.path.exists(os.path.join(_HERE, "_ref", "bench"))):
         subprocess.run(["make", "-C", _HERE, "ref_bench", f"REF_ROOT={ref_root}"], check=True,
                        capture_output=True)
-    if os.path.isdir(ref_root) and (force or not os.path.isdir(os.path.join(_HERE, "_ref", "cubins"))):
+    cubins = os.path.join(_HERE, "_ref", "cubins")
+    have_all = os.path.isdir(cubins) and os.path.exists(os.path.join(cubins, "igemm_online_quant_bf_128x256.sm_86.cubin"))
+    if os.path.isdir(ref_root) and (force or not have_all):
         # the reference's own kernels for sm_100a: GPU-side checker and "recompiled reference" baseline
         subprocess.run(["make", "-C", _HERE, "ref_cubins", f"REF_ROOT={ref_root}"], check=True,
                        capture_output=True)

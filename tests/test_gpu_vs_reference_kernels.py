@@ -71,3 +71,32 @@ def test_fp16_in_gemm_against_the_reference_kernel_at_4096():
     bound = (K // 32 + 2) * 2.0 ** -24 * 1.5 * (A.float().abs() @ B.float().abs())
     assert bool(((ours - ref).abs() <= bound).all())
     assert float((ours - ref).abs().max()) < 1e-2 and float(ref.abs().max()) > 10.0
+
+
+def test_fp16_in_gemm_with_256_column_blocks_against_the_reference_kernel():
+    """igemm_online_quant_bf_128x256 (128 x 256 tiles: one factor per 256 columns of B): the library with
+    col_block = 256 against the reference's own kernel, same bound as for the 128-column variants.
+
+    Rows 0 and 1 of every 128-row block are left out.  The reference kernel keeps its cross-warp reduction
+    scratch (`reduce_max`, 32 floats) in a union that overlays the first 128 bytes of its fp16 A tile
+    (igemm_online_quant_bf_128x256.cu:275-290), and its first-tile quantiser writes that scratch BEFORE it
+    converts the tile (:93-96 before :105-121): the first two rows of the first K tile are quantised from the
+    block maxima instead of from A.  No bench of the reference launches this kernel, so its output on those
+    rows is not a result anything depends on; every other row pins the 256-column arithmetic."""
+    M = N = K = 2048
+    g = torch.Generator(device="cuda").manual_seed(11)
+    A = (torch.rand((M, K), device=dev(), generator=g) * 2 - 1).half()
+    B = (torch.rand((K, N), device=dev(), generator=g) * 2 - 1).half()
+    ref = torch.zeros((M, N), dtype=torch.float32, device=dev())
+    RefKernel("igemm_online_quant_bf_128x256").launch(((N + 255) // 256, (M + 127) // 128), (512, 1), [A, B, ref, M, N, K])
+    ours = torch.full((M, N), -1.0, dtype=torch.float32, device=dev())
+    ig.igemm_online_quant_bf_128x256(A, B, ours, M, N, K)
+    assert_clean_status()
+    keep = (torch.arange(M, device=dev()) % 128) >= 2
+    bound = (K // 32 + 2) * 2.0 ** -24 * 1.5 * (A.float().abs() @ B.float().abs())
+    assert bool(((ours - ref).abs() <= bound)[keep].all())
+    assert float((ours - ref)[keep].abs().max()) < 1e-2 and float(ref.abs().max()) > 10.0
+    # the block width is part of the result: the 128-column arithmetic gives other numbers
+    other = torch.empty_like(ours)
+    ig.igemm_online_quant(A, B, other, M, N, K)
+    assert not torch.equal(other, ours)
