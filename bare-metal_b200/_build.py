@@ -17,7 +17,7 @@ NVCC_FLAGS = [
 
 HOST_DIR = os.path.join(PKG_DIR, "host")
 HOST_BIN = os.path.join(HOST_DIR, "bin")
-HOST_PROGRAMS = ("bench_igemm", "bench_sparse")
+HOST_PROGRAMS = ("bench_igemm", "bench_sparse", "bench_persistent")
 
 
 def build_host(force: bool = False) -> list[str]:
@@ -29,7 +29,7 @@ def build_host(force: bool = False) -> list[str]:
     out = []
     for name in HOST_PROGRAMS:
         src, exe = os.path.join(HOST_DIR, name + ".cpp"), os.path.join(HOST_BIN, name)
-        deps = [src, os.path.join(HOST_DIR, "host_common.h"), LIB_PATH]
+        deps = [src, os.path.join(HOST_DIR, "host_common.h"), os.path.join(HOST_DIR, "sparse_host.h"), LIB_PATH]
         if force or not os.path.exists(exe) or any(os.path.getmtime(d) > os.path.getmtime(exe) for d in deps):
             cmd = [nvcc, "-O2", "-std=c++17", "-I" + include, "-I" + HOST_DIR, "-o", exe, src, "-L" + LIB_DIR,
                    "-lbm_igemm", "-Xlinker", "-rpath," + "$ORIGIN/../../lib", "--cudart", "static"]

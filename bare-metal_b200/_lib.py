@@ -24,6 +24,7 @@ SIGNATURES = {
     "bm_w8a8_f16": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i64, _i, _p]),
     "bm_w8a8_f16_gather": (_i, [_p, _p, _p, _i, _i, _p, _p, _i, _i, _i, _i64, _i, _p]),
     "bm_gather_slab_f16": (_i, [_p, _i, _i, _i, _i, _i64, _p]),
+    "bm_peer_barrier": (_i, [_p, _i, _i, _p]),
     "bm_quantize_rows_f16": (_i, [_p, _p, _p, _i, _i, _p]),
     "bm_pack_b_kn_to_nk": (_i, [_p, _p, _i, _i, _p]),
     "bm_prune_2_4_i8": (_i, [_p, _p, _p, _i, _i, _p]),

@@ -475,18 +475,14 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
     int grid = num_tiles < resident ? num_tiles : resident;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    // Stream-K: the (tile, K block) units are dealt out evenly instead of whole tiles; a tile shared by
-    // several CTAs is finished by whichever arrives last (exact int32 sums parked in library scratch).
-    // Automatic (option "stream_k" = -1) for decode shapes whose row tiles would fill fewer than half of the
-    // CTA slots — a column slab of an N-split layer: 3584 channels are 28 tiles for 296 slots; every CTA then
-    // streams ~3 K blocks of one tile and fetches only that K range of the activations.  With enough row
-    // tiles whole tiles are kept: at N = 28672, K = 8192 stream-K was measured 1 % slower (33.5 vs 33.1 us),
-    // the parked sums add a dependent chain at the end.  1 forces it wherever it applies, 0 forbids it.
+    // Stream-K (option "stream_k" = 1): the (tile, K block) units are dealt out evenly instead of whole tiles; a
+    // tile shared by several CTAs is finished by whichever arrives last (exact int32 sums parked in library
+    // scratch).  Off unless asked for: the parked sums put a dependent chain — park, fence, count, re-read every
+    // part — at the very end of the launch, where nothing hides it.  Measured at N = 28672, K = 8192: 34.8 vs
+    // 26.5 us at 1 token, 45.5 vs 30.1 us at 64.
     p.sparse_rows = R;
     const long long units = static_cast<long long>(num_tiles) * p.k_blocks;
-    const int sk = opt(OPT_STREAM_K);
-    const bool sk_auto = sk < 0 && mode == 1 && p.tiles_c == 1 && 2 * num_tiles <= resident && p.k_blocks >= 4;
-    if ((sk > 0 || sk_auto) && units >= 2) {
+    if (opt(OPT_STREAM_K) > 0 && units >= 2) {
         grid = units < resident ? static_cast<int>(units) : resident;
         const int epi_warps = bn >= 128 ? 8 : 4;
         const size_t slice_ints = static_cast<size_t>(bn >= 128 ? bn / 2 : (bn == 64 ? 64 : 32)) * 32;
@@ -627,13 +623,28 @@ int bm_gather_slab_f16(uint16_t* const* D_peers, int n_peers, int self_index, in
     DeviceState* dev = nullptr;
     if (int rc = current_device_state(&dev)) return rc;
     const int row_bytes = n_len * 2;
-    const long long tiles = static_cast<long long>((M + 7) / 8) * ((row_bytes + 511) / 512);
-    const long long cap = static_cast<long long>(dev->sm_count) * 4;
+    const long long tiles = static_cast<long long>((M + 31) / 32) * ((row_bytes + 511) / 512);
+    const long long cap = static_cast<long long>(dev->sm_count) * 8;
     const int gbs = opt(OPT_GATHER_GBS);
     const unsigned cost = gbs > 0 ? static_cast<unsigned>((4096.0 * 16.0) / gbs + 0.5) : 0u;
     gather_slab_kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kGatherThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         dests, n_peers, self_index, M, row_bytes, static_cast<long long>(ldd) * 2, dev->link_clock, cost);
     BM_CUDA_TRY(cudaGetLastError());
+    return BM_OK;
+}
+
+int bm_peer_barrier(uint32_t* const* flag_arrays, int n_peers, int self_index, void* stream) {
+    if (!flag_arrays || n_peers <= 0 || n_peers > kGatherMaxPeers) return fail_msg(BM_ERR_NULL, "1 to 8 flag arrays are needed");
+    if (self_index < 0 || self_index >= n_peers) return fail_msg(BM_ERR_SHAPE, "self_index must be an index into flag_arrays");
+    BarrierFlags flags{};
+    for (int d = 0; d < n_peers; ++d) {
+        if (!flag_arrays[d] || (reinterpret_cast<uintptr_t>(flag_arrays[d]) & 3u)) return fail_msg(BM_ERR_ALIGN, "flag arrays must be 4-byte aligned");
+        flags.ptr[d] = flag_arrays[d];
+    }
+    DeviceState* dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    BM_CUDA_TRY(launch_pdl(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), 1, flags, n_peers,
+                           self_index, dev->status));
     return BM_OK;
 }
 

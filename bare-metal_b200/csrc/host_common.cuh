@@ -46,7 +46,7 @@ enum : int {
     OPT_DENSE_PAIR,          // 0 keeps dense problems on the single-CTA kernel
     OPT_SPARSE_PAIR,         // 0 keeps sparse problems on the single-CTA kernel
     OPT_ROW_BALANCED,        // decode shapes on packed weights: rows dealt out in multiples of 8 (0 = whole tiles)
-    OPT_STREAM_K,            // -1 automatic (few tiles, long K), 0 never, 1 whenever possible
+    OPT_STREAM_K,            // 1 deals (tile, K block) units to the CTAs instead of whole tiles (measured slower; off)
     OPT_TMA_STORE,           // 0 forces the direct-store epilogue
     OPT_DENSE_GROUP_M,       // -1 automatic; G >= 0 pins the band height of the pair kernel's tile order
     OPT_SPARSE_COL_FIRST,    // -1 automatic; 0 / 1 pins the tile order of the sparse pair kernel
@@ -60,7 +60,7 @@ inline const OptionSpec* option_specs() {
     static const OptionSpec specs[OPT_COUNT] = {
         {"force_bn", "BM_FORCE_BN", 0},           {"dense_pair", "BM_DENSE_PAIR", 1},
         {"sparse_pair", "BM_SPARSE_PAIR", 1},     {"row_balanced", "BM_ROW_BALANCED", 1},
-        {"stream_k", "BM_STREAM_K", -1},          {"tma_store", "BM_TMA_STORE", 1},
+        {"stream_k", "BM_STREAM_K", 0},           {"tma_store", "BM_TMA_STORE", 1},
         {"dense_group_m", "BM_DENSE_GROUP_M", -1}, {"sparse_col_first", "BM_SPARSE_COL_FIRST", -1},
         {"tail_narrow", "BM_TAIL_NARROW", 1},     {"pdl", "BM_PDL", 1},
         {"gather_gbs", "BM_GATHER_GBS", 680},

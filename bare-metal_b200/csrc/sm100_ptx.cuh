@@ -27,6 +27,7 @@ enum : int {
     DEV_TIMEOUT_EPI_ACC_FULL   = 4,   // epilogue waited for a finished accumulator
     DEV_TIMEOUT_DRAIN          = 5,   // teardown waited for copies / MMAs in flight
     DEV_TIMEOUT_SPLITK         = 6,   // split-K consumer waited for partial sums
+    DEV_TIMEOUT_PEER           = 7,   // group barrier waited for another GPU's flag
 };
 
 #ifndef BM_WAIT_LIMIT_NS

@@ -98,6 +98,16 @@ int bm_w8a8_f16_gather(const int8_t *X, const int8_t *W, uint16_t *const *D_peer
 int bm_gather_slab_f16(uint16_t *const *D_peers, int n_peers, int self_index, int M, int n_len,
                        int64_t ldd, void *stream);
 
+/* Group barrier for the step after a peer-store gather (no reference counterpart).  flag_arrays[d] is GPU d's
+ * array of 64 32-bit words in peer-mapped memory, all zero before the first round: words [0, n_peers) are written
+ * by the peers, word 32 is GPU d's own round counter.  Every call is one round: this GPU advances its counter on
+ * the device, writes the round number into word `self_index` of every other array and waits until the other GPUs
+ * have written theirs here — so every GPU of the group must make the same number of calls, and a call recorded in
+ * a CUDA graph stays correct when the graph is replayed.  One tiny kernel on `stream`, ordered behind the kernels
+ * already enqueued there (their stores to the peers are complete and visible before the flag goes out); its wait
+ * is bounded (1 s), a timeout is reported by bm_last_device_status as code 7. */
+int bm_peer_barrier(uint32_t *const *flag_arrays, int n_peers, int self_index, void *stream);
+
 /* Per-token dynamic quantisation fp16 -> int8, the step before the W8A8 GEMM.  B200 form of the
  * reference's online-quant kernels (igemm_online_quant.cu:144-150 take fp16 and quantise per K tile
  * with scale = max|x|/127); here one scale per row, arithmetic of the reference's host quantiser
@@ -239,7 +249,7 @@ int bm_last_device_status(int *code);
 /* Launcher options (tuning / testing switches; no reference counterpart — the reference fixes
  * launch geometry in its bench drivers, bench.cu:375-636).  Names: "force_bn" (pin the tile width;
  * 0 = choose), "dense_pair", "sparse_pair" (0 = single-CTA kernels only), "row_balanced",
- * "stream_k" (-1 automatic, 0 never, 1 wherever possible), "tma_store" (0 = direct-store
+ * "stream_k" (1 = stream-K work split of the sparse kernels; default 0), "tma_store" (0 = direct-store
  * epilogue), "dense_group_m", "sparse_col_first" (-1 automatic), "tail_narrow", "pdl", "gather_gbs".
  * Each starts from the environment variable BM_<NAME> read once at first use, else its default;
  * launchers never read the environment on the launch path.  Process-wide; set them while no

@@ -51,7 +51,8 @@ def check_sparse(dev, rank, world, M, N, K, seed, rows=None):
     c_slab, m_slab, sw_slab, n0, n_len = nsplit.shard_sparse_weights(
         torch.from_numpy(comp).to(dev), torch.from_numpy(nib).to(dev), torch.from_numpy(sw).to(dev), world, rank)
     tiled = ig.sp_pack_meta(m_slab, ig.BM_META_ROWS, n_len, K)
-    push = nsplit.ColumnShardedSparseLinear(c_slab, tiled, sw_slab, N, n0, mode="push")
+    packed = ig.sp_pack_weights(c_slab, m_slab, ig.BM_META_ROWS, n_len, K) if M <= 64 else None   # decode: packed blocks
+    push = nsplit.ColumnShardedSparseLinear(c_slab, tiled, sw_slab, N, n0, mode="push", W_packed_slab=packed)
     equal = len({l for _, l in push.slabs}) == 1
     for it in range(3):
         X = oracle.gen_int8((M, K), seed + it, 1)
