@@ -317,7 +317,9 @@ static int sparse_pair_left(int epi, bool f16, const void* S_comp, const uint8_t
     const size_t comp_bytes = static_cast<size_t>(K / 2) * elem;
     if (int rc = make_tensor_map_u8(&map_w, S_comp, comp_bytes, R, comp_bytes, 128, kBM, true)) return rc;
     const size_t units = meta_tiled_bytes(R, K) / 16;
-    if (int rc = make_tensor_map_u8(&map_e, meta_tiled, 16, units, 16, 16, f16 ? 128 : 256, false)) return rc;
+    // the tiled metadata is one contiguous run of 16-byte units: described as rows of 128 bytes, a box of 32 rows (16
+    // for fp16) lands in shared memory byte for byte as 256 (128) units would, with an eighth of the requests
+    if (int rc = make_tensor_map_u8(&map_e, meta_tiled, 128, units / 8, 128, 128, f16 ? 16 : 32, false)) return rc;
     const size_t row_bytes = static_cast<size_t>(Cn) * elem;
     if (int rc = make_tensor_map_u8(&map_x, B, row_bytes, K, row_bytes, 128, f16 ? 128 : kSpKLogical, true)) return rc;
     SparseParams p{};
@@ -387,7 +389,7 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
         CUtensorMap map_w, map_e, map_x;
         if (int rc = make_tensor_map_u8(&map_w, S_comp, K / 2, R, K / 2, 128, kBM, true)) return rc;
         const size_t units = meta_tiled_bytes(R, K) / 16;
-        if (int rc = make_tensor_map_u8(&map_e, meta_tiled, 16, units, 16, 16, 256, false)) return rc;
+        if (int rc = make_tensor_map_u8(&map_e, meta_tiled, 128, units / 8, 128, 128, 32, false)) return rc;   // see sparse_pair_left
         if (int rc = make_tensor_map_u8(&map_x, Dn, K, Cn, K, 128, kSpPairHalfN, true)) return rc;
         SparseParams p{};
         p.epi.out = out;

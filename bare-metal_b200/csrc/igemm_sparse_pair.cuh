@@ -2,7 +2,7 @@
 //
 // D^T = W_sparse * X^T with 256 output channels x 240 tokens per CTA pair.  CTA r of the pair
 // stages, per 256-wide K block: its 128 weight rows (kept values 128 x 128 B, TMA, 128-byte
-// swizzle), their 4 KiB of position metadata (one untiled TMA box of 256 x 16 B) and HALF of the
+// swizzle), their 4 KiB of position metadata (one untiled TMA box of 32 rows x 128 B over the contiguous tiled array) and HALF of the
 // token tile (120 rows x 256 B as two swizzled boxes) — 50 KiB per stage and CTA against 84 KiB for
 // a lone CTA with a 256-token tile.  The leader's MMA lane copies the metadata of BOTH CTAs into
 // tensor memory (tcgen05.cp.cta_group::2) and issues four sparse MMAs (M = 256, N = 240, K = 64
@@ -82,7 +82,7 @@ __device__ __forceinline__ void mma_f16_sp_pair(uint32_t d_tmem, uint64_t a_desc
         : "memory");
 }
 
-// map_w: kept values (byte map); map_e: tiled metadata as [units x 16 B] (box: 256 units, 128 for fp16);
+// map_w: kept values (byte map); map_e: tiled metadata as rows of 128 B = 8 units (box: 32 rows, 16 for fp16);
 // map_x: the dense operand — tokens [M x K] (K-major), or B[K x C] as a byte map when LEFT
 template <int EPI, bool LEFT = false, bool F16 = false>
 __global__ void __launch_bounds__(kDenseThreads, 1)
@@ -172,7 +172,7 @@ igemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kStageTx);
                     tma_load_2d_pair(a_smem0 + stage * kSpPairABytes, &map_w, leader_full, kb * 128, rb * 128);
                     tma_load_2d_pair(e_smem0 + stage * kSpMetaBytes, &map_e, leader_full, 0,
-                                     (rb * chunks_per_rb + kb * (F16 ? 1 : 2)) * 128);
+                                     (rb * chunks_per_rb + kb * (F16 ? 1 : 2)) * 16);       // a chunk = 128 units = 16 rows
                     const uint32_t b_addr = b_smem0 + stage * kSpPairBBytes;
                     if constexpr (F16) {
 #pragma unroll

@@ -514,7 +514,7 @@ def measure_link(cx, nsplit, _lib):
 
 
 def sharded_case(cx, nsplit, _lib, name, Mx, Nx, Kx, link_gbs, iters=20, with_nccl=True, single_ms=None):
-    """One dense W8A8 GEMM of a BASELINE shape, split by columns over the ranks: single-GPU time of the
+    """One dense W8A8 GEMM of the 8192-token layer, split by columns over the ranks: single-GPU time of the
     unsplit problem (same process, same run), slab GEMM alone, fused GEMM + gather (+ barrier), NCCL baseline;
     efficiencies = t_single / (N * t) and the fused step against its bound."""
     torch = cx.torch

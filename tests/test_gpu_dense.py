@@ -30,7 +30,7 @@ def run_i32(A, B_kn, layout, bn=None, guard=False):
 
 
 def test_config1_dense_1024_bit_exact_both_layouts():
-    """BASELINE config 1: M=N=K=1024, int8 uniform [-127,127], seed 0, int32 out, bit-exact."""
+    """The 1024^3 dense case: M=N=K=1024, int8 uniform [-127,127], seed 0, int32 out, bit-exact."""
     A = oracle.gen_int8((1024, 1024), 0, oracle.stream_id("C1", "A"))
     B = oracle.gen_int8((1024, 1024), 0, oracle.stream_id("C1", "B"))
     want = oracle.igemm(A, B, threads=0)

@@ -1,4 +1,4 @@
-"""BASELINE-size cases: sampled rows against the CPU oracle plus size-independent properties."""
+"""Full-size cases (4096^3 dense and 2:4 sparse, the 8192-token layer, the decode shapes): sampled rows against the CPU oracle plus size-independent properties."""
 import numpy as np
 import pytest
 import torch
@@ -16,7 +16,7 @@ def sample_rows(M, count, seed):
 
 
 def test_config2_w8a8_4096_sampled_rows_and_linearity():
-    """Config 2: M=N=K=4096, int8 uniform, sa/sw ~ U[1e-3,2e-2], fp16 out."""
+    """Dense W8A8 at full size: M=N=K=4096, int8 uniform, sa/sw ~ U[1e-3,2e-2], fp16 out."""
     M = N = K = 4096
     A = oracle.gen_int8((M, K), 0, oracle.stream_id("C2", "A"))
     W = oracle.gen_int8((N, K), 0, oracle.stream_id("C2", "W"))
@@ -50,7 +50,7 @@ def test_config2_w8a8_4096_sampled_rows_and_linearity():
 
 
 def test_config3_sparse_4096_equals_dense_product():
-    """Config 3: 2:4 sparse weights, int32 out must equal the dense product bit for bit."""
+    """2:4 sparse weights at M=N=K=4096, int32 out must equal the dense product bit for bit."""
     M = N = K = 4096
     comp, nib = oracle.gen_sparse_rows(N, K, 0, oracle.stream_id("C3", "W"))
     X = oracle.gen_int8((M, K), 0, oracle.stream_id("C3", "A"))
@@ -69,7 +69,7 @@ def test_config3_sparse_4096_equals_dense_product():
 
 @pytest.mark.parametrize("M", [1, 16, 64])
 def test_config5_decode_shapes(M):
-    """Config 5: K=8192, N=28672 sparse weights, M in {1,16,64}, fp16 out; every row checked."""
+    """Decode shapes: K=8192, N=28672 sparse weights, M in {1,16,64}, fp16 out; every row checked."""
     N, K = 28672, 8192
     comp, nib = oracle.gen_sparse_rows(N, K, 0, oracle.stream_id("C5", "W"))
     X = oracle.gen_int8((M, K), 0, oracle.stream_id("C5", f"X{M}"))
@@ -88,7 +88,7 @@ def test_config5_decode_shapes(M):
 
 
 def test_config4_layer_chain_shapes_sampled():
-    """Config 4: 8192 tokens, hidden 4096: QKV, out, gate+up, down projections, fp16 out."""
+    """The transformer-layer chain: 8192 tokens, hidden 4096: QKV, out, gate+up, down projections, fp16 out."""
     M = 8192
     rows = sample_rows(M, 6, 4)
     for name, K, N in (("qkv", 4096, 12288), ("out", 4096, 4096), ("gate_up", 4096, 22016), ("down", 11008, 4096)):

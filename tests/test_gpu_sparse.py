@@ -91,7 +91,7 @@ def test_sparse_left_rows_format(layout, M, N, K, bn):
                                       (128, 256, 512, 128), (256, 384, 1024, 256), (100, 200, 288, None),
                                       (3, 136, 96, None), (64, 1024, 2048, None), (300, 520, 800, None)])
 def test_sparse_weights_i32_and_f16(M, N, K, bn):
-    """Sparse WEIGHTS W[N,K] (config 3/5 convention): C = X @ W^T, int32 bit-exact, fp16 <= 1 ulp."""
+    """Sparse WEIGHTS W[N,K] (the convention of the sparse-weight workloads): C = X @ W^T, int32 bit-exact, fp16 <= 1 ulp."""
     comp, nib = oracle.gen_sparse_rows(N, K, 0, 21)
     X = oracle.gen_int8((M, K), 0, 22)
     want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
