@@ -421,17 +421,19 @@ def main() -> None:
     ev1.record()
     cx.sync()
     ms_total = ev0.elapsed_time(ev1)
-    # extra untimed load so the clock sampler has samples under load even for a short region
-    t_load = time.time()
-    j = 0
-    while not args.profile and time.time() - t_load < 1.5:
-        step(j); j += 1
-        if j % 64 == 0:
+    ms_step = cx.max_over_ranks(ms_total) / args.steps
+    # extra untimed load so the clock sampler has samples under load even for a short region.  The number of
+    # steps is the same on every rank (derived from the rank-agreed step time, never from a rank's own clock):
+    # a step of the N-split layer ends in a group barrier, and a rank that made one call more than its peers
+    # would wait in it for a round that never comes.
+    n_load = 0 if args.profile else max(64, min(40000, int(1.2 / max(ms_step * 1e-3, 1e-6))))
+    for j in range(n_load):
+        step(j)
+        if j % 64 == 63:
             torch.cuda.synchronize()
     cx.sync()
     t_wall1 = time.time()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
-    ms_step = cx.max_over_ranks(ms_total) / args.steps
     ops_step = 2.0 * M * N_TOTAL * K
     value = ops_step / (ms_step * 1e-3) / 1e12
     if args.profile:
