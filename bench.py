@@ -408,7 +408,7 @@ def main() -> None:
         sampler.start()
     # the ~0.3 s nvidia-smi needs to come up are spent under the same load, not idle: the timed steps then
     # run at the clocks and power state of a GPU that is doing this work, not of one waking up
-    for j in range(int(0.3 / max(1e-5, 1.2e-4)) if world == 1 else 600):
+    for j in range(0 if args.profile else (2500 if world == 1 else 600)):
         step(j)
         if j % 64 == 63:
             torch.cuda.synchronize()
