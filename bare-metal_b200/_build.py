@@ -18,6 +18,7 @@ NVCC_FLAGS = [
 HOST_DIR = os.path.join(PKG_DIR, "host")
 HOST_BIN = os.path.join(HOST_DIR, "bin")
 HOST_PROGRAMS = ("bench_igemm", "bench_sparse", "bench_persistent")
+DEVICE_TOOLS = ("linkprobe",)        # .cu programs with kernels of their own (sm_100a), no dependency on the library
 
 
 def build_host(force: bool = False) -> list[str]:
@@ -33,6 +34,16 @@ def build_host(force: bool = False) -> list[str]:
         if force or not os.path.exists(exe) or any(os.path.getmtime(d) > os.path.getmtime(exe) for d in deps):
             cmd = [nvcc, "-O2", "-std=c++17", "-I" + include, "-I" + HOST_DIR, "-o", exe, src, "-L" + LIB_DIR,
                    "-lbm_igemm", "-Xlinker", "-rpath," + "$ORIGIN/../../lib", "--cudart", "static"]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError("nvcc failed on " + name + ":\n" + res.stdout + res.stderr)
+        out.append(exe)
+    for name in DEVICE_TOOLS:
+        src, exe = os.path.join(HOST_DIR, name + ".cu"), os.path.join(HOST_BIN, name)
+        deps = [src, os.path.join(CSRC, "host_common.cuh"), os.path.join(CSRC, "sm100_ptx.cuh")]
+        if force or not os.path.exists(exe) or any(os.path.getmtime(d) > os.path.getmtime(exe) for d in deps):
+            cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", exe, src,
+                   "--cudart", "static"]
             res = subprocess.run(cmd, capture_output=True, text=True)
             if res.returncode != 0:
                 raise RuntimeError("nvcc failed on " + name + ":\n" + res.stdout + res.stderr)
