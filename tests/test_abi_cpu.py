@@ -78,3 +78,43 @@ def test_host_mirror_refuses_cpu_tensors():
     c = torch.zeros((128, 128), dtype=torch.float32)
     with pytest.raises(igemm.BmError):
         igemm.igemm_wmma(a, a, c, 128, 128, 64, 1.0, 1.0)
+
+
+def test_launcher_options_are_set_and_read_without_a_device():
+    """Options replace per-launch environment reads: known names round-trip, unknown names are refused, the
+    defaults are the documented ones, and a variable in the environment seeds its option once, at first use."""
+    import subprocess
+    import sys
+    L = _lib.load()
+    for name, default in (("force_bn", 0), ("dense_pair", 1), ("sparse_pair", 1), ("row_balanced", 1), ("stream_k", 0),
+                          ("tma_store", 1), ("dense_group_m", -1), ("sparse_col_first", -1), ("tail_narrow", 1),
+                          ("pdl", 1), ("gather_gbs", 680)):
+        if ("BM_" + name.upper()) not in os.environ:
+            assert _lib.get_option(name) == default, name
+    _lib.set_option("force_bn", 128)
+    assert _lib.get_option("force_bn") == 128
+    _lib.set_option("force_bn", 0)
+    v = C.c_int(0)
+    assert L.bm_set_option(b"no_such_option", 1) == -4 and L.bm_get_option(b"no_such_option", C.byref(v)) == -4
+    assert L.bm_set_option(None, 1) == -1
+    code = ("import sys; sys.path.insert(0, %r); from bare_metal_b200 import _lib; "
+            "print(_lib.get_option('gather_gbs'), _lib.get_option('force_bn'))" % ROOT)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120,
+                         env=dict(os.environ, BM_GATHER_GBS="555", BM_FORCE_BN="64"))
+    assert out.returncode == 0 and out.stdout.split() == ["555", "64"], out.stderr[-1000:]
+
+
+def test_gather_and_barrier_entry_points_reject_bad_arguments_without_a_device():
+    L = _lib.load()
+    buf = np.zeros(256, np.uint8)
+    a16 = (buf.ctypes.data + 15) & ~15
+    ptrs = (C.c_void_p * 2)(a16, a16)
+    assert L.bm_w8a8_f16_gather(a16, a16, None, 2, 0, a16, a16, 128, 128, 64, 256, _lib.BM_B_NK, None) == -1
+    assert L.bm_w8a8_f16_gather(a16, a16, ptrs, 2, 5, a16, a16, 128, 128, 64, 256, _lib.BM_B_NK, None) == -2
+    assert L.bm_gather_slab_f16(None, 2, 0, 8, 16, 32, None) == -1
+    assert L.bm_gather_slab_f16(ptrs, 2, 3, 8, 16, 32, None) == -2            # self index outside the list
+    assert L.bm_gather_slab_f16(ptrs, 2, 0, 8, 12, 32, None) == -3            # slab width not a multiple of 8
+    assert L.bm_gather_slab_f16(ptrs, 2, 0, 8, 64, 32, None) == -2            # pitch smaller than the slab
+    assert L.bm_peer_barrier(None, 2, 0, None) == -1
+    assert L.bm_peer_barrier(ptrs, 2, 2, None) == -2
+    assert L.bm_peer_barrier(ptrs, 9, 0, None) == -1

@@ -61,6 +61,24 @@ def _rank_main(rank, world, port, result_dir):
             ragged_refused = False
         except ValueError:
             ragged_refused = True
+        # the 2:4-sparse layer shares the sharding logic: slabs cut on 16 rows here, values + per-row positions
+        # + scales sliced together, the checker's sparse product standing in for the kernel
+        Ns, Ks = 96, 64
+        comp, nib = oracle.gen_sparse_rows(Ns, Ks, 0, 5)
+        sws = oracle.gen_scales(Ns, 0, 6)
+        Xs = oracle.gen_int8((M, Ks), 0, 7)
+        c_slab, m_slab, sw_s, n0s, n_lens = nsplit.shard_sparse_weights(torch.from_numpy(comp), torch.from_numpy(nib),
+                                                                       torch.from_numpy(sws), world, rank)
+
+        def cpu_sparse_gemm(Xt, Wc, Wm, D, sat, swt_, M_, n_, K_, ldd):
+            dense = oracle.decompress_rows(Wc.numpy(), Wm.numpy())
+            acc = oracle.igemm_nt(Xt.numpy(), dense, threads=1)
+            D.copy_(torch.from_numpy(oracle.dequant_w8a8_f16(acc, sat.numpy(), swt_.numpy())))
+
+        sp = nsplit.ColumnShardedSparseLinear(c_slab, m_slab, sw_s, Ns, n0s, mode="nccl", gemm=cpu_sparse_gemm)
+        got = nsplit.ColumnShardedSparseLinear.blocks_to_row_major(sp.forward(torch.from_numpy(Xs), torch.from_numpy(sa))).numpy()
+        want_s = oracle.dequant_w8a8_f16(oracle.igemm_nt(Xs, oracle.decompress_rows(comp, nib), threads=1), sa, sws)
+        ok = ok and np.array_equal(got.view(np.uint16), want_s.view(np.uint16)) and (n0s, n_lens) == nsplit.shard_columns(Ns, world, rank)
         open(os.path.join(result_dir, f"rank{rank}"), "w").write(f"{int(ok)} {int(ragged_refused)}")
     finally:
         dist.destroy_process_group()
