@@ -477,29 +477,17 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
     int grid = num_tiles < resident ? num_tiles : resident;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    // Stream-K (option "stream_k" = 1): the (tile, K block) units are dealt out evenly instead of whole tiles; a
-    // tile shared by several CTAs is finished by whichever arrives last (exact int32 sums parked in library
-    // scratch).  Off unless asked for: the parked sums put a dependent chain — park, fence, count, re-read every
-    // part — at the very end of the launch, where nothing hides it.  Measured at N = 28672, K = 8192: 34.8 vs
-    // 26.5 us at 1 token, 45.5 vs 30.1 us at 64.
+    // (Dealing out (tile, K block) units instead of whole tiles — stream-K, partial sums parked in global
+    // memory and finished by the last arrival — was measured slower on every decode shape and is not built:
+    // N = 28672, K = 8192: 34.8 vs 26.5 us at 1 token, 45.5 vs 30.1 us at 64.  The parked sums put a dependent
+    // chain — park, fence, count, re-read every part — at the very end of the launch, where nothing hides it.)
     p.sparse_rows = R;
-    const long long units = static_cast<long long>(num_tiles) * p.k_blocks;
-    if (opt(OPT_STREAM_K) > 0 && units >= 2) {
-        grid = units < resident ? static_cast<int>(units) : resident;
-        const int epi_warps = bn >= 128 ? 8 : 4;
-        const size_t slice_ints = static_cast<size_t>(bn >= 128 ? bn / 2 : (bn == 64 ? 64 : 32)) * 32;
-        const size_t ws_bytes = static_cast<size_t>(grid) * 2 * epi_warps * slice_ints * sizeof(int32_t);
-        if (int rc = ensure_split_k(dev, ws_bytes, static_cast<size_t>(num_tiles) * epi_warps)) return rc;
-        p.stream_k = 1;
-        p.sk_workspace = static_cast<int32_t*>(dev->sk_workspace);
-        p.sk_counters = dev->sk_counters;
-    }
 
     // Row-balanced tiles for the decode shapes (packed weights, all tokens in one column tile): whole
     // 128-row tiles would give some SMs two tiles and others one (224 tiles on 148 SMs); dealing the
     // rows out in multiples of 8 keeps every SM streaming the same number of bytes.  Option
     // "row_balanced" = 0 switches it off.
-    if (!p.stream_k && mode == 1 && packed && p.tiles_c == 1 && num_tiles % resident != 0 && R >= 8 * resident &&
+    if (mode == 1 && packed && p.tiles_c == 1 && num_tiles % resident != 0 && R >= 8 * resident &&
         opt(OPT_ROW_BALANCED) != 0) {
         p.row_balanced = 1;
         grid = resident;
@@ -854,11 +842,7 @@ int bm_last_device_status(int* code) {
     if (int rc = current_device_state(&dev)) return rc;
     BM_CUDA_TRY(cudaDeviceSynchronize());
     BM_CUDA_TRY(cudaMemcpy(code, dev->status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (*code != 0) {
-        BM_CUDA_TRY(cudaMemset(dev->status, 0, sizeof(int)));
-        // an aborted stream-K launch may have left arrival counters half-way
-        if (dev->sk_counters) BM_CUDA_TRY(cudaMemset(dev->sk_counters, 0, dev->sk_counter_ints * sizeof(int)));
-    }
+    if (*code != 0) BM_CUDA_TRY(cudaMemset(dev->status, 0, sizeof(int)));
     // launches of the no-alloc entry point record their give-ups in a word of their own
     int fixed = 0;
     if (int rc = noalloc_read_status(&fixed)) return rc;
@@ -928,8 +912,6 @@ void bm_shutdown(void) {
         if (cudaSetDevice(d) == cudaSuccess) {
             cudaFree(s.status);
             cudaFree(s.scratch);
-            cudaFree(s.sk_workspace);
-            cudaFree(s.sk_counters);
         }
         cudaSetDevice(prev);
         s = DeviceState{};

@@ -184,55 +184,6 @@ __device__ __forceinline__ void drain_accumulator(const EpilogueParams& p, uint3
 }
 
 // ------------------------------------------------------------------------------------------------
-// Split-K support: a CTA that computed only part of a tile's K range parks its raw int32 sums in
-// global memory, laid out [column][lane] so that each store / load instruction of a warp is one
-// contiguous 128-byte line; the part that arrives last adds all parts up and runs the epilogue.
-// ------------------------------------------------------------------------------------------------
-template <int NC>
-__device__ __forceinline__ void park_accumulator(uint32_t taddr, int32_t* dst, int lane) {
-    constexpr int CHUNKS = NC / 32;
-    uint32_t ra[32], rb[32];
-    tmem_ld_32x32(taddr, ra);
-#pragma unroll
-    for (int c = 0; c < CHUNKS; c += 2) {
-        tmem_ld_wait();
-        if (c + 1 < CHUNKS) tmem_ld_32x32(taddr + (c + 1) * 32, rb);
-#pragma unroll
-        for (int k = 0; k < 32; ++k) __stcg(dst + (c * 32 + k) * 32 + lane, static_cast<int32_t>(ra[k]));
-        if (c + 1 < CHUNKS) {
-            tmem_ld_wait();
-            if (c + 2 < CHUNKS) tmem_ld_32x32(taddr + (c + 2) * 32, ra);
-#pragma unroll
-            for (int k = 0; k < 32; ++k) __stcg(dst + ((c + 1) * 32 + k) * 32 + lane, static_cast<int32_t>(rb[k]));
-        }
-    }
-}
-
-// `part_ptr(i)` gives this warp's slice of part i.
-template <int EPI, int NC, bool TRANSPOSED, class PartPtr>
-__device__ __forceinline__ void finish_parked(const EpilogueParams& p, PartPtr part_ptr, int parts,
-                                              int lane_coord, int cross0, int cross_limit, const EpiStrip<NC>* strip,
-                                              float lane_s, int lane) {
-    constexpr int CHUNKS = NC / 32;
-#pragma unroll 1
-    for (int c = 0; c < CHUNKS; ++c) {
-        if (cross0 + c * 32 >= cross_limit) break;
-        uint32_t r[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) r[k] = 0;
-        for (int part = 0; part < parts; ++part) {
-            const int32_t* s = part_ptr(part) + c * 32 * 32 + lane;
-#pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] += static_cast<uint32_t>(__ldcg(s + k * 32));
-        }
-        if constexpr (TRANSPOSED)
-            emit_col_chunk<EPI>(p, lane_coord, cross0 + c * 32, cross_limit, r, strip->scale + c * 32, lane_s);
-        else
-            emit_row_chunk<EPI>(p, lane_coord, cross0 + c * 32, r, strip->scale + c * 32, strip->zero + c * 32, lane_s);
-    }
-}
-
-// ------------------------------------------------------------------------------------------------
 // TMA-store drain (normal orientation).  Direct stores from the accumulator layout make every
 // lane of a warp write a different output ROW (16 bytes each, a pitch apart); with power-of-two
 // pitches those land on few L2 slices and the drain, not the MMA, bounds the tile.  Here each warp

@@ -46,7 +46,6 @@ enum : int {
     OPT_DENSE_PAIR,          // 0 keeps dense problems on the single-CTA kernel
     OPT_SPARSE_PAIR,         // 0 keeps sparse problems on the single-CTA kernel
     OPT_ROW_BALANCED,        // decode shapes on packed weights: rows dealt out in multiples of 8 (0 = whole tiles)
-    OPT_STREAM_K,            // 1 deals (tile, K block) units to the CTAs instead of whole tiles (measured slower; off)
     OPT_TMA_STORE,           // 0 forces the direct-store epilogue
     OPT_DENSE_GROUP_M,       // -1 automatic; G >= 0 pins the band height of the pair kernel's tile order
     OPT_SPARSE_COL_FIRST,    // -1 automatic; 0 / 1 pins the tile order of the sparse pair kernel
@@ -60,10 +59,9 @@ inline const OptionSpec* option_specs() {
     static const OptionSpec specs[OPT_COUNT] = {
         {"force_bn", "BM_FORCE_BN", 0},           {"dense_pair", "BM_DENSE_PAIR", 1},
         {"sparse_pair", "BM_SPARSE_PAIR", 1},     {"row_balanced", "BM_ROW_BALANCED", 1},
-        {"stream_k", "BM_STREAM_K", 0},           {"tma_store", "BM_TMA_STORE", 1},
-        {"dense_group_m", "BM_DENSE_GROUP_M", -1}, {"sparse_col_first", "BM_SPARSE_COL_FIRST", -1},
-        {"tail_narrow", "BM_TAIL_NARROW", 1},     {"pdl", "BM_PDL", 1},
-        {"gather_gbs", "BM_GATHER_GBS", 680},
+        {"tma_store", "BM_TMA_STORE", 1},         {"dense_group_m", "BM_DENSE_GROUP_M", -1},
+        {"sparse_col_first", "BM_SPARSE_COL_FIRST", -1}, {"tail_narrow", "BM_TAIL_NARROW", 1},
+        {"pdl", "BM_PDL", 1},                     {"gather_gbs", "BM_GATHER_GBS", 680},
     };
     return specs;
 }
@@ -99,10 +97,6 @@ struct DeviceState {
     unsigned long long* link_clock = nullptr;   // device word: virtual clock of the NVLink store pacer (same allocation)
     void* scratch = nullptr;        // library-owned staging (tiled metadata for reference-format calls)
     size_t scratch_bytes = 0;
-    void* sk_workspace = nullptr;   // split-K partial sums (stream-K launches)
-    size_t sk_workspace_bytes = 0;
-    int* sk_counters = nullptr;     // split-K arrival counters, kept at zero between launches
-    size_t sk_counter_ints = 0;
 };
 
 inline std::mutex& state_mutex() {
@@ -157,33 +151,6 @@ inline int ensure_scratch(DeviceState* s, size_t bytes) {
     }
     BM_CUDA_TRY(cudaMalloc(&s->scratch, bytes));
     s->scratch_bytes = bytes;
-    return BM_OK;
-}
-
-// grow-only split-K buffers of the current device (counters are zero-filled when (re)allocated)
-inline int ensure_split_k(DeviceState* s, size_t workspace_bytes, size_t counter_ints) {
-    std::lock_guard<std::mutex> lock(state_mutex());
-    if (s->sk_workspace_bytes < workspace_bytes) {
-        if (s->sk_workspace) {
-            BM_CUDA_TRY(cudaDeviceSynchronize());
-            BM_CUDA_TRY(cudaFree(s->sk_workspace));
-            s->sk_workspace = nullptr;
-            s->sk_workspace_bytes = 0;
-        }
-        BM_CUDA_TRY(cudaMalloc(&s->sk_workspace, workspace_bytes));
-        s->sk_workspace_bytes = workspace_bytes;
-    }
-    if (s->sk_counter_ints < counter_ints) {
-        if (s->sk_counters) {
-            BM_CUDA_TRY(cudaDeviceSynchronize());
-            BM_CUDA_TRY(cudaFree(s->sk_counters));
-            s->sk_counters = nullptr;
-            s->sk_counter_ints = 0;
-        }
-        BM_CUDA_TRY(cudaMalloc(&s->sk_counters, counter_ints * sizeof(int)));
-        BM_CUDA_TRY(cudaMemset(s->sk_counters, 0, counter_ints * sizeof(int)));
-        s->sk_counter_ints = counter_ints;
-    }
     return BM_OK;
 }
 

@@ -69,10 +69,6 @@ struct SparseParams {
     const uint8_t* meta_tiled;         // tiled metadata, or the packed weight blocks when PACKED
     int tiles_r, tiles_c, k_blocks;    // row blocks of the sparse operand, column tiles of the dense one
     int* status;
-    // stream-K (decode shapes): the (tile, k-block) units are dealt out evenly to the CTAs, so a tile
-    // may be shared by several CTAs; partial sums meet in `sk_workspace`, the part that arrives last
-    // (per epilogue warp, counted in `sk_counters`) adds them up and runs the epilogue.  No CTA waits.
-    int stream_k;
     // row-balanced mode (packed weights, one column tile — the decode shapes): the rows of the
     // sparse operand are dealt out evenly in multiples of 8, so a CTA's last tile may hold fewer
     // than 128 rows and only those rows are fetched (the packed blocks are row-contiguous).
@@ -82,29 +78,22 @@ struct SparseParams {
     // a tile of the dense operand), 1 = column tiles fastest (consecutive pairs share a block of the
     // sparse operand — for weights larger than L2 and few column tiles, so each block leaves HBM once)
     int col_first;
-    int* sk_counters;                  // [tiles][epilogue warps], zero between launches (self-resetting)
-    int32_t* sk_workspace;             // [CTAs][2: head / tail share][epilogue warps][NC x 32]
 };
 
-// One contiguous piece of work: k-blocks [kb0, kb1) of one tile; the tile covers rows
-// [row0, row0 + nrows) of the sparse operand (nrows = 128 except in row-balanced mode).
+// One piece of work: a tile over its whole K range; the tile covers rows [row0, row0 + nrows) of the
+// sparse operand (nrows = 128 except in row-balanced mode).
 struct WorkSegment {
-    int tile, kb0, kb1, row0, nrows;
+    int tile, row0, nrows;
 };
 
-// Deals work to CTA `cta` of `ctas`.  Static mode: whole tiles cta, cta+ctas, ...  Stream-K mode: the
-// units [cta*U/ctas, (cta+1)*U/ctas) of the U = tiles*k_blocks (tile-major) units, cut at tile borders.
+// Deals work to CTA `cta` of `ctas`: whole tiles cta, cta+ctas, ..., or (row-balanced mode) one
+// contiguous range of rows cut into tiles of at most 128.
 struct WorkIter {
-    long long u, u_end;
-    int tile, tiles, k_blocks, step, tiles_r;
+    int tile, tiles, step, tiles_r;
     int row, row_end;                  // row-balanced mode
-    bool stream_k, row_balanced;
+    bool row_balanced;
     __device__ WorkIter(const SparseParams& p, int cta, int ctas, int tiles_)
-        : tile(cta), tiles(tiles_), k_blocks(p.k_blocks), step(ctas), tiles_r(p.tiles_r),
-          stream_k(p.stream_k != 0), row_balanced(p.row_balanced != 0) {
-        const long long U = static_cast<long long>(tiles_) * p.k_blocks;
-        u = U * cta / ctas;
-        u_end = U * (cta + 1) / ctas;
+        : tile(cta), tiles(tiles_), step(ctas), tiles_r(p.tiles_r), row_balanced(p.row_balanced != 0) {
         const long long r8 = (p.sparse_rows + 7) / 8;
         row = static_cast<int>(r8 * cta / ctas) * 8;
         row_end = static_cast<int>(r8 * (cta + 1) / ctas) * 8;
@@ -113,38 +102,19 @@ struct WorkIter {
         if (row_balanced) {
             if (row >= row_end) return false;
             s.tile = 0;
-            s.kb0 = 0;
-            s.kb1 = k_blocks;
             s.row0 = row;
             s.nrows = row_end - row < 128 ? row_end - row : 128;
             row += s.nrows;
             return true;
         }
-        s.nrows = 128;
-        if (stream_k) {
-            if (u >= u_end) return false;
-            s.tile = static_cast<int>(u / k_blocks);
-            s.kb0 = static_cast<int>(u % k_blocks);
-            const long long left = u_end - u;
-            s.kb1 = (s.kb0 + left < k_blocks) ? static_cast<int>(s.kb0 + left) : k_blocks;
-            s.row0 = (s.tile % tiles_r) * 128;
-            u += s.kb1 - s.kb0;
-            return true;
-        }
         if (tile >= tiles) return false;
         s.tile = tile;
-        s.kb0 = 0;
-        s.kb1 = k_blocks;
         s.row0 = (tile % tiles_r) * 128;
+        s.nrows = 128;
         tile += step;
         return true;
     }
 };
-
-// CTA that owns unit `u` under the stream-K split: the largest i with floor(i*U/ctas) <= u.
-__device__ __forceinline__ int stream_k_owner(long long u, long long U, int ctas) {
-    return static_cast<int>(((u + 1) * ctas - 1) / U);
-}
 
 // F16 = true turns the same pipeline into the FP16 2:4 GEMM of kernels/gemm/hgemm_sparse
 // (hgemm_sparse_tiled.cu:122-129: fp16 A_comp[M x K/2], fp16 B[K x N], fp32 C): in BYTES a stage
@@ -233,9 +203,8 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                 // Decode shapes: every CTA walks the K blocks of its tile from a different starting block and wraps
                 // around (exact integer sums do not care about the order).  All CTAs read the SAME few tokens; in
                 // lockstep they would all ask the L2 for the same 16 KiB of activations at the same moment.
-                const bool whole_k = seg.kb0 == 0 && seg.kb1 == p.k_blocks;
-                const int rot = (ROTATE_K && whole_k) ? static_cast<int>((blockIdx.x * 7u) % static_cast<unsigned>(p.k_blocks)) : 0;
-                for (int kb_seq = seg.kb0; kb_seq < seg.kb1; ++kb_seq) {
+                const int rot = ROTATE_K ? static_cast<int>((blockIdx.x * 7u) % static_cast<unsigned>(p.k_blocks)) : 0;
+                for (int kb_seq = 0; kb_seq < p.k_blocks; ++kb_seq) {
                     const int kb = kb_seq + rot < p.k_blocks ? kb_seq + rot : kb_seq + rot - p.k_blocks;
                     if (!bounded_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
@@ -304,7 +273,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                                   DEV_TIMEOUT_MMA_ACC_EMPTY)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!bounded_wait(full_bar(stage), phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
                         ok = false;
                         break;
@@ -329,7 +298,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                             // K = 64 consumes); a K = 32 fp16 MMA takes one column of the pair, chosen by
                             // the selector in bits [0,2) of the instruction descriptor
                             mma_f16_sp(d_tmem, a_desc, b_desc, e_tmem + (ks & ~1), idesc | static_cast<uint32_t>(ks & 1),
-                                       (kb != seg.kb0 || ks != 0) ? 1u : 0u);
+                                       (kb != 0 || ks != 0) ? 1u : 0u);
                             continue;
                         } else if constexpr (DENSE_MN) {
                             b_desc = make_smem_desc(b_addr + ks * (64 * 128), 128 * kSpKLogical, 1024,
@@ -338,7 +307,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                             b_desc = make_smem_desc(b_addr + (ks >> 1) * (BN * 128) + (ks & 1) * 64, 0, 1024,
                                                     SWIZZLE_128B_DESC);
                         }
-                        mma_i8_sp(d_tmem, a_desc, b_desc, e_tmem + 2 * ks, idesc, (kb != seg.kb0 || ks != 0) ? 1u : 0u);
+                        mma_i8_sp(d_tmem, a_desc, b_desc, e_tmem + 2 * ks, idesc, (kb != 0 || ks != 0) ? 1u : 0u);
                     }
                     tc_commit(empty_bar(stage));
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -373,52 +342,16 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             // never write past this tile's own columns when the tile is narrower than a 32-column chunk
             int c_limit = TRANSPOSED ? p.epi.rows : p.epi.cols;
             if (BN < 32 && c_limit > c0 + BN) c_limit = c0 + BN;
-            const bool whole = (seg.kb0 == 0 && seg.kb1 == p.k_blocks);
             stage_strip<EPI, Cfg::NC, TRANSPOSED>(p.epi, strip, c0, lane);
             const float lane_s = lane_scale_of<EPI, TRANSPOSED>(p.epi, lane_coord);
             if (!bounded_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPI_ACC_FULL))
                 break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * Cfg::NC;
-            if (whole) {
-                drain_accumulator<EPI, Cfg::NC, TRANSPOSED>(epi, taddr, lane_coord, c0, c_limit, strip, lane_s);
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty_bar(acc));
-            } else {
-                // a share of a tile: park the raw sums, then see whether this warp's slice is complete
-                // A CTA's range holds at most two shares: the tail of the tile its range starts in
-                // ("head" slot 0) and the head of the tile it ends in (slot 1).
-                const long long U = static_cast<long long>(num_tiles) * p.k_blocks;
-                const int G = static_cast<int>(gridDim.x);
-                const long long u_first = static_cast<long long>(seg.tile) * p.k_blocks;
-                const int cta_first = stream_k_owner(u_first, U, G);
-                const int parts = stream_k_owner(u_first + p.k_blocks - 1, U, G) - cta_first + 1;
-                constexpr int SLICE = Cfg::NC * 32;
-                auto share_of = [&](int cta) -> int32_t* {
-                    const int which = (static_cast<int>((U * cta / G) / p.k_blocks) == seg.tile) ? 0 : 1;
-                    return p.sk_workspace +
-                           ((static_cast<size_t>(cta) * 2 + which) * Cfg::EPI_WARPS + (warp - 2)) * SLICE;
-                };
-                park_accumulator<Cfg::NC>(taddr, share_of(static_cast<int>(blockIdx.x)), lane);
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty_bar(acc));        // tensor memory is free again
-                __threadfence();
-                int last = 0;
-                int* counter = p.sk_counters + seg.tile * Cfg::EPI_WARPS + (warp - 2);
-                if (lane == 0) {
-                    last = (atomicAdd(counter, 1) == parts - 1);
-                    if (last) *counter = 0;                            // ready for the next launch
-                }
-                last = __shfl_sync(0xFFFFFFFFu, last, 0);
-                if (last) {
-                    __threadfence();
-                    finish_parked<EPI, Cfg::NC, TRANSPOSED>(
-                        epi, [&](int part) -> const int32_t* { return share_of(cta_first + part); }, parts,
-                        lane_coord, c0, c_limit, strip, lane_s, lane);
-                }
-            }
+            drain_accumulator<EPI, Cfg::NC, TRANSPOSED>(epi, taddr, lane_coord, c0, c_limit, strip, lane_s);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
             if (++acc == Cfg::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
         }
     }

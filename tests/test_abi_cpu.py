@@ -86,7 +86,7 @@ def test_launcher_options_are_set_and_read_without_a_device():
     import subprocess
     import sys
     L = _lib.load()
-    for name, default in (("force_bn", 0), ("dense_pair", 1), ("sparse_pair", 1), ("row_balanced", 1), ("stream_k", 0),
+    for name, default in (("force_bn", 0), ("dense_pair", 1), ("sparse_pair", 1), ("row_balanced", 1),
                           ("tma_store", 1), ("dense_group_m", -1), ("sparse_col_first", -1), ("tail_narrow", 1),
                           ("pdl", 1), ("gather_gbs", 680)):
         if ("BM_" + name.upper()) not in os.environ:

@@ -170,47 +170,6 @@ def test_packed_sparse_weights_match_oracle(M, N, K, bn):
     assert torch.equal(packed, packed2)
 
 
-@pytest.mark.parametrize("M,N,K,bn", [(1, 384, 2048, 16), (16, 1152, 4096, 16), (64, 640, 1536, 64),
-                                      (40, 200, 800, None), (256, 512, 2048, 128), (8, 28672, 1024, None)])
-def test_stream_k_split_matches_oracle(M, N, K, bn):
-    """K ranges of a tile shared between CTAs (stream-K): partial sums are added exactly, whatever
-    the split; run twice so the self-resetting arrival counters are exercised."""
-    from _gpu import options
-    comp, nib = oracle.gen_sparse_rows(N, K, 3, 41)
-    X = oracle.gen_int8((M, K), 3, 42)
-    want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
-    packed = ig.sp_pack_weights(T(comp), T(nib), ig.BM_META_ROWS, N, K)
-    sa, sw = oracle.gen_scales(M, 3, 3), oracle.gen_scales(N, 3, 4)
-    want16 = oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)
-    with options(stream_k=1), forced_bn(bn):
-        for _ in range(2):
-            C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
-            ig.w8a8_sparse_i32_packed(T(X), packed, C, M, N, K)
-            assert_clean_status()
-            assert np.array_equal(C.cpu().numpy(), want)
-            D = torch.zeros((M, N), dtype=torch.float16, device=dev())
-            ig.w8a8_sparse_linear_packed(T(X), packed, D, T(sa), T(sw), M, N, K)
-            assert_clean_status()
-            assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1
-    # the static schedule gives the same integers
-    with options(stream_k=0), forced_bn(bn):
-        C2 = torch.empty((M, N), dtype=torch.int32, device=dev())
-        ig.w8a8_sparse_i32_packed(T(X), packed, C2, M, N, K)
-        assert np.array_equal(C2.cpu().numpy(), want)
-
-
-def test_stream_k_reference_left_orientation():
-    from _gpu import options
-    M, N, K = 384, 256, 2048
-    dense, comp, meta, B = bench_sparse_inputs(M, N, K)
-    want = oracle.igemm(dense, B, threads=0)
-    with options(stream_k=1):
-        C = torch.full((M, N), -7, dtype=torch.int32, device=dev())
-        ig.igemm_sparse_i32(T(comp), T(meta.view(np.int32)), ig.BM_META_REF, T(B), C, M, N, K, ig.BM_B_KN)
-        assert_clean_status()
-    assert np.array_equal(C.cpu().numpy(), want)
-
-
 @pytest.mark.parametrize("M,N,K", [(240, 256, 256), (100, 130, 288), (400, 520, 1056), (500, 512, 4096), (1000, 1100, 544)])
 def test_sparse_weights_on_cta_pairs(M, N, K):
     """Sparse weights on the CTA-pair kernel (tcgen05.mma.sp.cta_group::2, 256 channels x 240 tokens)."""
@@ -245,7 +204,7 @@ def test_row_balanced_decode_tiles(M, N, K):
     sa, sw = oracle.gen_scales(M, 5, 3), oracle.gen_scales(N, 5, 4)
     want16 = oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)
     for balanced in (1, 0):
-        with options(row_balanced=balanced, stream_k=0):
+        with options(row_balanced=balanced):
             guard = torch.full((M + 2, N), 0x5A5A5A5A, dtype=torch.int32, device=dev())
             ig.w8a8_sparse_i32_packed(T(X), packed, guard[1:M + 1], M, N, K)
             assert_clean_status()
