@@ -241,7 +241,7 @@ static size_t meta_tiled_bytes(int R, int K) {
 }
 
 static int pack_meta(const void* meta_in, int fmt, void* tiled, int R, int K, cudaStream_t stream,
-                     size_t block_stride = kSpMetaBytes, size_t block_offset = 0) {
+                     bool into_packed_weights = false) {
     if (!meta_in || !tiled) return fail_msg(BM_ERR_NULL, "metadata pointer is NULL");
     if (R <= 0 || K <= 0 || K % (fmt == BM_META_REF_F16 ? 16 : 32) != 0)
         return fail_msg(BM_ERR_SHAPE, "K must be a positive multiple of 32 (16 for the fp16 reference format)");
@@ -252,21 +252,22 @@ static int pack_meta(const void* meta_in, int fmt, void* tiled, int R, int K, cu
     const int k_blocks = ceil_div(K, kSpKLogical);
     const size_t units = meta_tiled_bytes(R, K) / 16;
     const unsigned blocks = static_cast<unsigned>((units + 255) / 256);
+    const MetaDest dest{k_blocks, into_packed_weights ? ceil_div(R, 128) * 128 : 0};
     if (fmt == BM_META_ROWS || fmt == BM_META_ROWS_F16)
         pack_meta_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(meta_in),
                                                           static_cast<uint8_t*>(tiled), R, K, k_blocks, units,
-                                                          block_stride, block_offset, fmt == BM_META_ROWS_F16 ? 1 : 0);
+                                                          dest, fmt == BM_META_ROWS_F16 ? 1 : 0);
     else if (fmt == BM_META_REF)
         pack_meta_ref_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(meta_in),
                                                          static_cast<uint8_t*>(tiled), R, K, k_blocks, units,
-                                                         block_stride, block_offset);
+                                                         dest);
     else if (fmt == BM_META_REF_F16)
         pack_meta_ref_f16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(meta_in),
                                                              static_cast<uint8_t*>(tiled), R, K, k_blocks, units,
-                                                             block_stride, block_offset);
-    else if (fmt == BM_META_TILED && block_stride != kSpMetaBytes)
+                                                             dest);
+    else if (fmt == BM_META_TILED && into_packed_weights)
         pack_meta_copy_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(meta_in),
-                                                          static_cast<uint8_t*>(tiled), units, block_stride, block_offset);
+                                                          static_cast<uint8_t*>(tiled), units, dest);
     else
         return fail_msg(BM_ERR_LAYOUT, "unknown metadata format tag");
     BM_CUDA_TRY(cudaGetLastError());
@@ -807,7 +808,7 @@ int bm_w8a8_sparse_f16(const int8_t* X, const int8_t* W_comp, const void* W_meta
 
 size_t bm_sp_packed_weight_bytes(int N, int K) {
     if (N <= 0 || K <= 0) return 0;
-    return static_cast<size_t>(ceil_div(N, 128)) * ceil_div(K, kSpKLogical) * kSpPackedBlock;
+    return static_cast<size_t>(ceil_div(N, 128)) * 128 * ceil_div(K, kSpKLogical) * kSpPackedRowBytes;
 }
 
 int bm_sp_pack_weights(const int8_t* W_comp, const void* W_meta, int meta_format, void* W_packed, int N, int K,
@@ -819,9 +820,9 @@ int bm_sp_pack_weights(const int8_t* W_comp, const void* W_meta, int meta_format
     const int k_blocks = ceil_div(K, kSpKLogical);
     const size_t chunks = static_cast<size_t>(ceil_div(N, 128)) * k_blocks * 1024;
     pack_comp_blocks_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(
-        W_comp, static_cast<uint8_t*>(W_packed), N, K, k_blocks, chunks, kSpPackedBlock);
+        W_comp, static_cast<uint8_t*>(W_packed), N, K, k_blocks, chunks, ceil_div(N, 128) * 128);
     BM_CUDA_TRY(cudaGetLastError());
-    return pack_meta(W_meta, meta_format, W_packed, N, K, stream, kSpPackedBlock, 16384);
+    return pack_meta(W_meta, meta_format, W_packed, N, K, stream, true);
 }
 
 int bm_w8a8_sparse_i32_packed(const int8_t* X, const void* W_packed, int32_t* C, int M, int N, int K, int64_t ldc,

@@ -62,7 +62,12 @@ struct SparseCfg {
     static_assert(COLS_NEEDED <= 512, "tensor memory over-subscribed");
 };
 
-constexpr int kSpPackedBlock = 16384 + kSpMetaBytes;   // packed weights: swizzled values + metadata per block
+// Packed weights (what the decode-shaped GEMM streams): for every 256-wide K block kb one slice of
+// rows_padded x 160 bytes — first the compressed values of ALL rows (128 B per row, pre-swizzled), then the
+// metadata of all rows in groups of 8 rows (256 B per group: the 16 bytes of K half 0 of the 8 rows, then
+// those of K half 1).  Any range of rows that starts on a multiple of 8 is then two contiguous pieces per K
+// block, whatever 128-row block it starts in: one bulk copy of values and one of metadata per pipeline stage.
+constexpr int kSpPackedRowBytes = 160;
 
 struct SparseParams {
     EpilogueParams epi;
@@ -71,7 +76,7 @@ struct SparseParams {
     int* status;
     // row-balanced mode (packed weights, one column tile — the decode shapes): the rows of the
     // sparse operand are dealt out evenly in multiples of 8, so a CTA's last tile may hold fewer
-    // than 128 rows and only those rows are fetched (the packed blocks are row-contiguous).
+    // than 128 rows and only those rows are fetched (packed weights are row-contiguous within a K block).
     int row_balanced;
     int sparse_rows;                   // rows of the sparse operand (R)
     // tile order of the pair kernel: 0 = row blocks of the sparse operand fastest (consecutive pairs share
@@ -191,15 +196,12 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             WorkSegment seg;
             while (ok && work.next(seg)) {
                 const int r0 = seg.row0;
-                const int rb = r0 / kBM;                   // first 128-row block the tile touches
-                const int off0 = r0 % kBM;                 // rows of that block skipped (row-balanced mode only)
-                const int n0 = seg.nrows < kBM - off0 ? seg.nrows : kBM - off0;   // rows from block rb
-                const int n1 = seg.nrows - n0;                                    // rows from block rb + 1
                 const int c0 = (seg.tile / p.tiles_r) * BN;
                 // tiled metadata is laid out in 4 KiB blocks of 256 logical K; an fp16 k-block is half of one
-                const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(rb) *
-                                                             (F16 ? (p.k_blocks + 1) / 2 : p.k_blocks) *
-                                                             (PACKED ? kSpPackedBlock : kSpMetaBytes);
+                const uint8_t* meta_row = p.meta_tiled + static_cast<size_t>(r0 / kBM) *
+                                                             (F16 ? (p.k_blocks + 1) / 2 : p.k_blocks) * kSpMetaBytes;
+                // packed weights: one slice of (padded rows) x 160 bytes per K block, values first
+                const size_t rows_padded = static_cast<size_t>(p.tiles_r) * kBM;
                 // Decode shapes: every CTA walks the K blocks of its tile from a different starting block and wraps
                 // around (exact integer sums do not care about the order).  All CTAs read the SAME few tokens; in
                 // lockstep they would all ask the L2 for the same 16 KiB of activations at the same moment.
@@ -210,20 +212,14 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                                       DEV_TIMEOUT_PRODUCER_EMPTY)) { ok = false; break; }
                     const uint32_t bar = full_bar(stage);
                     if constexpr (PACKED) {
-                        // pre-swizzled, row-contiguous blocks: linear copies of exactly the rows of this tile
-                        // (row0 is a multiple of 8, so the swizzle phase of a row is the same in the tile)
-                        mbar_expect_tx(bar, static_cast<uint32_t>(seg.nrows) * (128 + 32) + Cfg::B_BYTES);
-                        const uint8_t* blk0 = meta_row + static_cast<size_t>(kb) * kSpPackedBlock;
-                        const uint8_t* blk1 = blk0 + static_cast<size_t>(p.k_blocks) * kSpPackedBlock;
-                        const uint32_t a_dst = a_smem0 + stage * Cfg::A_BYTES;
-                        const uint32_t e_dst = e_smem0 + stage * kSpMetaBytes;
-                        bulk_load(a_dst, blk0 + off0 * 128, n0 * 128, bar);
-                        if (n1 > 0) bulk_load(a_dst + n0 * 128, blk1, n1 * 128, bar);
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            bulk_load(e_dst + j * 2048, blk0 + Cfg::A_BYTES + j * 2048 + off0 * 16, n0 * 16, bar);
-                            if (n1 > 0) bulk_load(e_dst + j * 2048 + n0 * 16, blk1 + Cfg::A_BYTES + j * 2048, n1 * 16, bar);
-                        }
+                        // pre-swizzled and row-contiguous within the K block: one linear copy of the values and
+                        // one of the metadata of exactly the rows of this tile (row0 is a multiple of 8, so the
+                        // swizzle phase of a row in the tile is the one it was packed with)
+                        mbar_expect_tx(bar, static_cast<uint32_t>(seg.nrows) * kSpPackedRowBytes + Cfg::B_BYTES);
+                        const uint8_t* slice = p.meta_tiled + static_cast<size_t>(kb) * rows_padded * kSpPackedRowBytes;
+                        bulk_load(a_smem0 + stage * Cfg::A_BYTES, slice + static_cast<size_t>(r0) * 128, seg.nrows * 128, bar);
+                        bulk_load(e_smem0 + stage * kSpMetaBytes, slice + rows_padded * 128 + static_cast<size_t>(r0) * 32,
+                                  seg.nrows * 32, bar);
                     } else {
                         mbar_expect_tx(bar, Cfg::A_BYTES + Cfg::B_BYTES + kMetaStage);
                         tma_load_2d(a_smem0 + stage * Cfg::A_BYTES, &map_s, bar, kb * 128, r0);
@@ -286,7 +282,9 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                     // metadata: rows are 16 B apart, 8-row groups 128 B apart, no swizzle
 #pragma unroll
                     for (int j = 0; j < (F16 ? 1 : 2); ++j)
-                        tmem_cp_128x128b(e_tmem + 4 * j, make_smem_desc(e_addr + j * 2048, 0, 128, SWIZZLE_NONE_DESC));
+                        tmem_cp_128x128b(e_tmem + 4 * j,
+                                         PACKED ? make_smem_desc(e_addr + j * 128, 0, 256, SWIZZLE_NONE_DESC)   // halves interleaved per 8 rows
+                                                : make_smem_desc(e_addr + j * 2048, 0, 128, SWIZZLE_NONE_DESC));
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
                         const uint64_t a_desc = make_smem_desc(a_addr + ks * 32, 0, 1024, SWIZZLE_128B_DESC);

@@ -8,6 +8,8 @@
 #pragma once
 #include <cstdint>
 
+#include "igemm_sparse.cuh"      // kSpPackedRowBytes
+
 namespace bm {
 
 // Tiled order: [row block rb][k-block kb][chunk j in 0..1][row r in 0..127][16 bytes].
@@ -24,11 +26,19 @@ __device__ __forceinline__ void tiled_coords(size_t unit, int k_blocks, int& row
     k_byte0 = (kb * 2 + j) * 16;                    // first metadata byte of this row's 16
 }
 
-// Where unit u of the tiled metadata goes: blocks of 4 KiB (256 units) that are either packed back
-// to back (block_stride = 4096, block_offset = 0) or embedded in the 20 KiB blocks of the packed
-// weight format (block_stride = 20480, block_offset = 16384).
-__device__ __forceinline__ size_t meta_unit_offset(size_t unit, size_t block_stride, size_t block_offset) {
-    return (unit >> 8) * block_stride + block_offset + (unit & 255) * 16;
+// Where unit u of the tiled metadata goes: blocks of 4 KiB (256 units) packed back to back
+// (rows_padded = 0), or the metadata part of the packed weight format above.
+struct MetaDest {
+    int k_blocks;
+    int rows_padded;                // 0: plain tiled blocks; else rows of the packed weights (multiple of 128)
+};
+__device__ __forceinline__ size_t meta_unit_offset(size_t unit, const MetaDest& d) {
+    if (d.rows_padded == 0) return unit * 16;
+    const size_t blk = unit >> 8;
+    const size_t kb = blk % d.k_blocks, rb = blk / d.k_blocks;
+    const size_t j = (unit >> 7) & 1, row = rb * 128 + (unit & 127);
+    return kb * static_cast<size_t>(d.rows_padded) * kSpPackedRowBytes + static_cast<size_t>(d.rows_padded) * 128 +
+           (row >> 3) * 256 + j * 128 + (row & 7) * 16;
 }
 
 // How tcgen05.mma.sp.kind::f16 reads its metadata (found by probing single nibbles on a B200): within
@@ -47,7 +57,7 @@ __device__ __forceinline__ uint32_t lane_word(const NatWord& nat, int row, int q
 // per-row nibble bytes [R x K/8] -> tiled; one thread per 16-byte unit
 __global__ void pack_meta_rows_kernel(const uint8_t* __restrict__ rows_meta, uint8_t* __restrict__ tiled,
                                       int R, int K, int k_blocks, size_t units,
-                                      size_t block_stride, size_t block_offset, int f16_lanes) {
+                                      MetaDest dest, int f16_lanes) {
     const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (unit >= units) return;
     int row, b0;
@@ -62,14 +72,14 @@ __global__ void pack_meta_rows_kernel(const uint8_t* __restrict__ rows_meta, uin
     uint32_t w[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) w[q] = lane_word(nat, row, q, f16_lanes);
-    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, block_stride, block_offset)) =
+    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, dest)) =
         make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // reference uint32 words -> tiled; one thread per 16-byte unit (4 K steps of 32)
 __global__ void pack_meta_ref_kernel(const uint32_t* __restrict__ meta_ref, uint8_t* __restrict__ tiled,
                                      int R, int K, int k_blocks, size_t units,
-                                     size_t block_stride, size_t block_offset) {
+                                     MetaDest dest) {
     const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (unit >= units) return;
     int row, b0;
@@ -83,7 +93,7 @@ __global__ void pack_meta_ref_kernel(const uint32_t* __restrict__ meta_ref, uint
                    ? meta_ref[(static_cast<size_t>(row / 16) * k_steps + s) * 8 + (row % 16) % 8]
                    : 0x44444444u;
     }
-    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, block_stride, block_offset)) =
+    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, dest)) =
         make_uint4(w[0], w[1], w[2], w[3]);
 }
 
@@ -92,7 +102,7 @@ __global__ void pack_meta_ref_kernel(const uint32_t* __restrict__ meta_ref, uint
 // kind::f16; one thread per 16-byte unit = 8 K steps of 16
 __global__ void pack_meta_ref_f16_kernel(const uint32_t* __restrict__ meta_ref, uint8_t* __restrict__ tiled,
                                          int R, int K, int k_blocks, size_t units,
-                                         size_t block_stride, size_t block_offset) {
+                                         MetaDest dest) {
     const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (unit >= units) return;
     int row, b0;
@@ -113,26 +123,26 @@ __global__ void pack_meta_ref_f16_kernel(const uint32_t* __restrict__ meta_ref, 
     uint32_t w[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) w[q] = lane_word(nat, row, q, 1);
-    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, block_stride, block_offset)) =
+    *reinterpret_cast<uint4*>(tiled + meta_unit_offset(unit, dest)) =
         make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// tiled metadata (4 KiB blocks) -> the metadata part of packed weight blocks
+// tiled metadata (4 KiB blocks) -> the metadata part of packed weights
 __global__ void pack_meta_copy_kernel(const uint8_t* __restrict__ tiled_in, uint8_t* __restrict__ packed,
-                                      size_t units, size_t block_stride, size_t block_offset) {
+                                      size_t units, MetaDest dest) {
     const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (unit >= units) return;
-    *reinterpret_cast<uint4*>(packed + meta_unit_offset(unit, block_stride, block_offset)) =
+    *reinterpret_cast<uint4*>(packed + meta_unit_offset(unit, dest)) =
         *reinterpret_cast<const uint4*>(tiled_in + unit * 16);
 }
 
-// Compressed 2:4 values comp[R x K/2] -> packed weight blocks.  Block (rb, kb) holds rows
-// [128 rb, +128) x compressed bytes [128 kb, +128) as 128 rows x 128 B laid out exactly as a TMA load
-// with 128-byte swizzle would leave them in shared memory (16-byte chunk c of row r sits at
-// r*128 + ((c ^ (r & 7)) << 4)), so the GEMM can fetch the whole 16 KiB with one linear bulk copy.
+// Compressed 2:4 values comp[R x K/2] -> the values part of packed weights.  Within K block kb, row r holds
+// compressed bytes [128 kb, +128) laid out exactly as a TMA load with 128-byte swizzle would leave the row in
+// shared memory when the copied range starts on a multiple of 8 rows (16-byte chunk c of row r sits at
+// r*128 + ((c ^ (r & 7)) << 4)), so the GEMM fetches any such range with one linear bulk copy.
 // Rows / bytes beyond the operand are zero.  One thread per 16-byte chunk.
 __global__ void pack_comp_blocks_kernel(const int8_t* __restrict__ comp, uint8_t* __restrict__ packed,
-                                        int R, int K, int k_blocks, size_t chunks, size_t block_stride) {
+                                        int R, int K, int k_blocks, size_t chunks, int rows_padded) {
     const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (idx >= chunks) return;
     const int c = static_cast<int>(idx & 7);
@@ -146,7 +156,8 @@ __global__ void pack_comp_blocks_kernel(const int8_t* __restrict__ comp, uint8_t
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row < R && byte0 < row_bytes)
         v = *reinterpret_cast<const uint4*>(comp + static_cast<size_t>(row) * row_bytes + byte0);
-    *reinterpret_cast<uint4*>(packed + blk * block_stride + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+    *reinterpret_cast<uint4*>(packed + static_cast<size_t>(kb) * rows_padded * kSpPackedRowBytes +
+                              static_cast<size_t>(row) * 128 + ((c ^ (r & 7)) << 4)) = v;
 }
 
 // Magnitude pruning of a dense int8 matrix W[R x K] to 2:4 along K, compression included: of every

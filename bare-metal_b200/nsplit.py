@@ -20,6 +20,12 @@ i+1, which every rank enqueues after whatever it enqueued to read result i.  So:
 on the stream it was produced on (or order the other stream before the next call), and do not
 keep it across more than one further call of the same layer.
 
+Two steps in flight: `forward_fused(..., lane=0 or 1)` names the output buffer AND the barrier
+instance of the call, so independent steps (different micro-batches) may run on two streams, lane 0
+on one and lane 1 on the other — the GEMM of one step then overlaps the NVLink tail and the barrier
+of the other.  Calls of one lane must be ordered on one stream; every rank must issue the same
+lanes in the same order; result of lane l stays valid until the next call on lane l.
+
 One process per GPU (torchrun); `torch.distributed` carries the rendezvous only.
 """
 from __future__ import annotations
@@ -72,7 +78,7 @@ class GroupBarrier:
     higher cost (measured 9.5 us against 6 us per step on two B200s)."""
     _cache = {}
 
-    def __init__(self, group, device):
+    def __init__(self, group, device):     # collective: every rank of the group constructs it at the same point
         import torch.distributed._symmetric_memory as symm_mem
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
@@ -84,16 +90,25 @@ class GroupBarrier:
         self.ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.hdl.buffer_ptrs])
 
     @classmethod
-    def of(cls, group, device):
-        key = (id(group), str(device))
+    def of(cls, group, device, lane: int = 0):
+        """The group's barrier of `lane`: lanes are independent instances (own flags, own round counter), one per
+        stream that runs steps of its own."""
+        key = (id(group), str(device), lane)
         if key not in cls._cache:
             cls._cache[key] = cls(group, device)
         return cls._cache[key]
 
-    def __call__(self):
+    def __call__(self, stream=None):
         from . import _lib
-        rc = _lib.load().bm_peer_barrier(self.ptrs, self.world, self.rank, torch.cuda.current_stream().cuda_stream)
+        rc = _lib.load().bm_peer_barrier(self.ptrs, self.world, self.rank, _stream_handle(stream))
         _lib.check(rc, "bm_peer_barrier")
+
+
+def _stream_handle(stream):
+    """cudaStream_t of `stream` (a torch stream, a raw handle, or None = torch's current stream)."""
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
 
 
 class _Sharded:
@@ -117,8 +132,9 @@ class _Sharded:
         if mode == "nccl" and len({l for _, l in lens}) != 1:
             raise ValueError("the NCCL all-gather path needs equal slabs; use the peer-store path for ragged splits")
 
-    def _symmetric(self, M, device):
-        """The symmetric [M x N_total] output to fill next, its handle and the slab pointers (two per key, in turn)."""
+    def _symmetric(self, M, device, lane=None):
+        """The symmetric [M x N_total] output to fill next, its handle and the slab pointers: two per key, used in
+        turn, or the one `lane` names."""
         key = (M, str(device))
         if key not in self._sym:
             import torch.distributed._symmetric_memory as symm_mem
@@ -129,6 +145,8 @@ class _Sharded:
                 pair.append((buf, hdl, self._peer_slab_pointers(hdl)))   # + the slab's first column in every rank's buffer
             self._sym[key] = pair
             self._turn[key] = 0
+        if lane is not None:
+            return self._sym[key][lane]
         turn = self._turn[key]
         self._turn[key] = turn ^ 1
         return self._sym[key][turn]
@@ -187,19 +205,21 @@ class ColumnShardedLinear(_Sharded):
         return out
 
     # ---- fused GEMM + gather ---------------------------------------------------------------
-    def forward_fused(self, X, sa, barrier: bool = True):
+    def forward_fused(self, X, sa, barrier: bool = True, lane=None, stream=None):
         """Returns this rank's row-major [M x N] output, complete once the trailing barrier has run
-        (see the module text for how long it stays valid)."""
+        (see the module text for how long it stays valid).  `lane` (0 / 1) pins the output buffer and the
+        barrier instance, for two steps in flight on two streams; `stream` is where the step is enqueued
+        (default: torch's current stream)."""
         from . import _lib, igemm
         M = X.shape[0]
-        buf, _, slab_ptrs = self._symmetric(M, X.device)
+        buf, _, slab_ptrs = self._symmetric(M, X.device, lane)
         L = _lib.load()
         rc = L.bm_w8a8_f16_gather(X.data_ptr(), self.W.data_ptr(), slab_ptrs, self.world, self.rank, sa.data_ptr(),
                                   self.sw.data_ptr(), M, self.n_len, self.K, self.n_total, igemm.BM_B_NK,
-                                  torch.cuda.current_stream().cuda_stream)
+                                  _stream_handle(stream))
         _lib.check(rc, "bm_w8a8_f16_gather")
-        if barrier:
-            GroupBarrier.of(self.group, X.device)()     # every rank's stores are complete before anyone reads
+        if barrier:     # every rank's stores are complete before anyone reads
+            GroupBarrier.of(self.group, X.device, lane or 0)(stream)
         return buf
 
     def forward(self, X, sa):

@@ -314,6 +314,8 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the sparse / decode / layer-chain side measurements")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: fused = GEMM epilogue stores to all ranks over NVLink; nccl = GEMM then all-gather")
+    ap.add_argument("--lanes", type=int, default=2, choices=[1, 2],
+                    help="N > 1, fused gather: steps in flight (2 = consecutive steps alternate between two streams)")
     ap.add_argument("--workload", default="dense", choices=["dense", "sparse", "decode", "online_quant", "hgemm_sparse"],
                     help="with --profile: which kernel to run (dense = the headline; sparse = 2:4 at 4096^3; "
                          "decode = the skinny sparse GEMM)")
@@ -369,9 +371,15 @@ def main() -> None:
     sa_d, sw_d = torch.from_numpy(sa_h).to(devn), torch.from_numpy(sw_h).to(devn)
     D_d = [torch.empty((M, n_len), dtype=torch.float16, device=devn) for _ in range(n_sets)]
     layer = G_blocks = None
+    lanes = None
     if world > 1:
         layer = nsplit.ColumnShardedLinear(W_d[0], sw_d, N_TOTAL, n0, mode=args.gather)
         G_blocks = torch.empty((world, M, n_len), dtype=torch.float16, device=devn)
+        # two steps in flight: consecutive steps are independent problems (rotating operand sets, the layer's two
+        # output buffers), so they alternate between two streams — the GEMM of one step overlaps the NVLink tail
+        # and the group barrier of the other, as a server does with independent micro-batches
+        if args.gather == "fused" and args.lanes == 2:
+            lanes = [torch.cuda.Stream(), torch.cuda.Stream()]
 
     def step(i: int):
         s = i % n_sets
@@ -379,9 +387,21 @@ def main() -> None:
             ig.w8a8_linear(A_d[s], W_d[s], D_d[s], sa_d, sw_d, M, n_len, K)
             return D_d[s]
         layer.W = W_d[s]
+        if lanes is not None:
+            return layer.forward_fused(A_d[s], sa_d, lane=i & 1, stream=lanes[i & 1])
         if args.gather == "fused":
             return layer.forward_fused(A_d[s], sa_d)
         return layer.forward_nccl(A_d[s], sa_d, out=G_blocks, local=D_d[s])
+
+    def fork_lanes(ev):
+        """The lane streams start behind `ev` (recorded on the current stream)."""
+        for ln in lanes or ():
+            ln.wait_event(ev)
+
+    def join_lanes():
+        """The current stream continues behind everything enqueued on the lane streams."""
+        for ln in lanes or ():
+            torch.cuda.current_stream().wait_stream(ln)
 
     def gemm_only(i: int):
         s = i % n_sets
@@ -416,8 +436,10 @@ def main() -> None:
     cx.sync()
     t_wall0 = time.time()
     ev0.record()
+    fork_lanes(ev0)
     for i in range(args.steps):
         step(i)
+    join_lanes()
     ev1.record()
     cx.sync()
     ms_total = ev0.elapsed_time(ev1)
@@ -492,8 +514,10 @@ def main() -> None:
         else:
             par = f"n-split x{world} ({n_len} of {N_TOTAL} weight columns per GPU)" + (
                 " + all-gather of the fp16 output fused into the GEMM epilogue (paced peer TMA stores) + group barrier"
+                + ("; two steps in flight (independent steps alternate between two streams, two output buffers)"
+                   if lanes is not None else "")
                 if args.gather == "fused" else " + NCCL all-gather of the fp16 output")
-            launches = args.steps
+            launches = args.steps * (2 if args.gather == "fused" else 1)     # per rank: GEMM+gather kernel, barrier kernel
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong" if world > 1 else "weak",
@@ -589,14 +613,21 @@ def sharded_headline_detail(cx, nsplit, _lib, layer, step, gemm_only, A_d, W_d, 
     def fused_nobar(i):
         s = i % n_sets
         layer.W = W_d[s]; layer.forward_fused(A_d[s], sa_d, barrier=False)
+    def fused_serial(i):
+        s = i % n_sets
+        layer.W = W_d[s]; layer.forward_fused(A_d[s], sa_d)
     t_nccl = cx.timeit(nccl, max(5, args.steps // 2), collective=True)
     t_kernel = cx.timeit(fused_nobar, args.steps, collective=True)
+    cx.sync()
+    t_serial = cx.timeit(fused_serial, args.steps, collective=True)      # one step at a time on one stream
     cx.sync()
     recv = 2.0 * M * (N_TOTAL - n_len)
     t_link = recv / (link * 1e9) * 1e3
     target = max(kern_ms, t_link)
     return {"single_gpu_ms": single_ms, "gemm_only_ms": kern_ms, "gemm_only_efficiency": single_ms / (cx.world * kern_ms),
             "gathered_ms": ms_step, "gathered_efficiency": single_ms / (cx.world * ms_step),
+            "steps_in_flight": args.lanes if args.gather == "fused" else 1,
+            "single_step_latency_ms": t_serial,
             "fused_kernel_without_barrier_ms": t_kernel, "nccl_all_gather_ms": t_nccl,
             "fused_collective": {"bound": "nvlink receive" if t_link > kern_ms else "tensor",
                                  "recv_bytes_per_rank": recv, "link_gb_per_s": link,

@@ -227,9 +227,11 @@ int bm_w8a8_sparse_f16(const int8_t *X, const int8_t *W_comp, const void *W_meta
                        const float *sa_m, const float *sw_n, int M, int N, int K, int64_t ldd,
                        void *stream);
 
-/* Packed sparse weights: per (128-row block, 256-wide K block) one contiguous 20 KiB block —
- * 16 KiB of kept values already in the shared-memory order of the kernel, then 4 KiB of tiled
- * metadata — so a decode-shaped GEMM streams the weights from HBM strictly sequentially.
+/* Packed sparse weights: per 256-wide K block one slice of (N padded to 128) x 160 bytes — the kept
+ * values of every row (128 B per row, already in the shared-memory order of the kernel), then the
+ * metadata of every row in 8-row groups — so a decode-shaped GEMM fetches ANY range of rows that
+ * starts on a multiple of 8 with two linear copies per K block (values, metadata).  An opaque
+ * library format: only bm_sp_pack_weights writes it, only the _packed entry points read it.
  * One-time repack (no reference counterpart; the reference only compresses, sparse_meta_int8.h:116). */
 size_t bm_sp_packed_weight_bytes(int N, int K);
 int bm_sp_pack_weights(const int8_t *W_comp, const void *W_meta, int meta_format, void *W_packed,
