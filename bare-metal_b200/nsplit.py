@@ -20,11 +20,13 @@ i+1, which every rank enqueues after whatever it enqueued to read result i.  So:
 on the stream it was produced on (or order the other stream before the next call), and do not
 keep it across more than one further call of the same layer.
 
-Two steps in flight: `forward_fused(..., lane=0 or 1)` names the output buffer AND the barrier
-instance of the call, so independent steps (different micro-batches) may run on two streams, lane 0
-on one and lane 1 on the other — the GEMM of one step then overlaps the NVLink tail and the barrier
-of the other.  Calls of one lane must be ordered on one stream; every rank must issue the same
-lanes in the same order; result of lane l stays valid until the next call on lane l.
+Two steps in flight: `forward_fused(..., lane=0 or 1)` names the pair of output buffers AND the
+barrier instance of the call, so independent steps (different micro-batches) may run on two streams,
+lane 0 on one and lane 1 on the other — the GEMM of one step then overlaps the NVLink tail and the
+barrier of the other.  Calls of one lane must be ordered on one stream; every rank must issue the
+same lanes in the same order; the rule above holds per lane (a lane's call i+2 reuses the buffer of
+its call i, behind the lane's barrier i+1), so read a result on its lane's stream before that
+lane's next call is enqueued, or order the reader before it.
 
 One process per GPU (torchrun); `torch.distributed` carries the rendezvous only.
 """
@@ -133,9 +135,10 @@ class _Sharded:
             raise ValueError("the NCCL all-gather path needs equal slabs; use the peer-store path for ragged splits")
 
     def _symmetric(self, M, device, lane=None):
-        """The symmetric [M x N_total] output to fill next, its handle and the slab pointers: two per key, used in
-        turn, or the one `lane` names."""
-        key = (M, str(device))
+        """The symmetric [M x N_total] output to fill next, its handle and the slab pointers.  Every lane owns two
+        buffers, used in turn (lane None is lane 0); a lane's pair is allocated at its first use — a collective
+        step, like everything else here done by all ranks in the same order."""
+        key = (M, str(device), lane or 0)
         if key not in self._sym:
             import torch.distributed._symmetric_memory as symm_mem
             pair = []
@@ -145,8 +148,6 @@ class _Sharded:
                 pair.append((buf, hdl, self._peer_slab_pointers(hdl)))   # + the slab's first column in every rank's buffer
             self._sym[key] = pair
             self._turn[key] = 0
-        if lane is not None:
-            return self._sym[key][lane]
         turn = self._turn[key]
         self._turn[key] = turn ^ 1
         return self._sym[key][turn]
@@ -207,8 +208,8 @@ class ColumnShardedLinear(_Sharded):
     # ---- fused GEMM + gather ---------------------------------------------------------------
     def forward_fused(self, X, sa, barrier: bool = True, lane=None, stream=None):
         """Returns this rank's row-major [M x N] output, complete once the trailing barrier has run
-        (see the module text for how long it stays valid).  `lane` (0 / 1) pins the output buffer and the
-        barrier instance, for two steps in flight on two streams; `stream` is where the step is enqueued
+        (see the module text for how long it stays valid).  `lane` (0 / 1) picks the lane's pair of output
+        buffers and its barrier instance, for two steps in flight on two streams; `stream` is where the step is enqueued
         (default: torch's current stream)."""
         from . import _lib, igemm
         M = X.shape[0]

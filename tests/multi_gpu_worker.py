@@ -43,6 +43,35 @@ def check_dense(dev, rank, world, M, N, K, seed, rows=None, nccl=True):
     assert ig.last_device_status() == 0, "a bounded device-side wait gave up"
 
 
+def check_dense_two_in_flight(dev, rank, world, M, N, K, seed, steps=6):
+    """Independent steps alternating between two streams (lane = output buffer + barrier instance): every step has
+    activations of its own, results are read only after all steps were enqueued, two steps back at most."""
+    W = oracle.gen_int8((N, K), seed, 2)
+    sw = oracle.gen_scales(N, seed, 4)
+    W_slab, sw_slab, n0, n_len = nsplit.shard_weights(torch.from_numpy(W).to(dev), torch.from_numpy(sw).to(dev), world, rank)
+    layer = nsplit.ColumnShardedLinear(W_slab, sw_slab, N, n0, mode="fused")
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    Xs = [oracle.gen_int8((M, K), seed + 100 + i, 1) for i in range(steps)]
+    sas = [oracle.gen_scales(M, seed + 100 + i, 3) for i in range(steps)]
+    Xd = [torch.from_numpy(x).to(dev) for x in Xs]
+    sad = [torch.from_numpy(a).to(dev) for a in sas]
+    torch.cuda.synchronize()
+    kept = {}
+    for i in range(steps):
+        lane = i & 1
+        out = layer.forward_fused(Xd[i], sad[i], lane=lane, stream=streams[lane])
+        if i >= steps - 2:                   # the last result of each lane is still valid after the loop
+            kept[i] = out
+        else:                                # earlier ones: copy on the lane's stream before the lane is reused
+            with torch.cuda.stream(streams[lane]):
+                kept[i] = out.clone()
+    torch.cuda.synchronize()
+    for i, out in kept.items():
+        want = oracle.dequant_w8a8_f16(oracle.igemm_nt(Xs[i], W), sas[i], sw).view(np.uint16)
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), want), f"rank {rank}: step {i} of two in flight differs"
+    assert ig.last_device_status() == 0, "a bounded device-side wait gave up"
+
+
 def check_sparse(dev, rank, world, M, N, K, seed, rows=None):
     """2:4-sparse weights, N-split: local sparse GEMM + peer-store gather (and the NCCL path for equal slabs)."""
     comp, nib = oracle.gen_sparse_rows(N, K, seed, 5)
@@ -88,6 +117,8 @@ def main():
         check_dense(dev, rank, world, 777, 344 * world, 640, 20)
         # enough tiles for several waves of CTA pairs and a partly filled last one
         check_dense(dev, rank, world, 2304, 2560 * world, 256, 30)
+        # two independent steps in flight on two streams
+        check_dense_two_in_flight(dev, rank, world, 1024, 512 * world, 512, 35)
         # 2:4-sparse layers: decode shapes (1 and 64 tokens; 3584 channels per rank at full size) and a prefill chunk
         check_sparse(dev, rank, world, 1, 448 * world, 1024, 40)
         check_sparse(dev, rank, world, 64, 448 * world, 2048, 50)
