@@ -274,11 +274,11 @@ static int pack_meta(const void* meta_in, int fmt, void* tiled, int R, int K, cu
     return BM_OK;
 }
 
-template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false>
+template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false, int ROWS = kBM>
 static int launch_sparse_inst(const CUtensorMap& ms, const CUtensorMap& md, const SparseParams& p, int grid,
                               cudaStream_t stream) {
-    using Cfg = SparseCfg<BN>;
-    auto kern = igemm_sparse_kernel<BN, DENSE_MN, TRANSPOSED, EPI, PACKED>;
+    using Cfg = SparseCfg<BN, ROWS>;
+    auto kern = igemm_sparse_kernel<BN, DENSE_MN, TRANSPOSED, EPI, PACKED, false, ROWS>;
     static ConfiguredFlags flags;
     if (int rc = ensure_smem_limit(flags, kern, Cfg::SMEM_BYTES)) return rc;
     BM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, 1, ms, md, p));
@@ -493,6 +493,17 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
         p.row_balanced = 1;
         grid = resident;
     }
+    // Few rows per CTA (the slab of an N-split layer: 3584 channels on 296 CTA slots are 8-16 rows each): ring
+    // stages sized for 32 or 64 rows instead of 128, so up to 12 K blocks are in flight per CTA instead of 4 —
+    // a CTA walks ALL K blocks of its rows one after the other, and with a 4-deep ring that walk is 8 memory
+    // round trips long however few bytes it moves.  Option "decode_tile_rows" = 128 keeps the full stages.
+    int tile_rows = 128;
+    if (p.row_balanced && bn <= 64) {
+        const int per_cta = ceil_div(ceil_div(R, 8), grid) * 8;
+        tile_rows = per_cta <= 32 ? 32 : per_cta <= 64 ? 64 : 128;
+        const int forced = opt(OPT_DECODE_TILE_ROWS);
+        if (forced == 32 || forced == 64 || forced == 128) tile_rows = forced;
+    }
 
 #define BM_SP(BNV, MN, TR, E) return launch_sparse_inst<BNV, MN, TR, E>(map_s, map_d, p, grid, stream)
     if (mode == 0) {
@@ -507,6 +518,15 @@ static int sparse_gemm(int mode, int epi, const int8_t* S_comp, const uint8_t* m
         }
     } else if (!dense_mn && packed) {
 #define BM_SPP(BNV, E) return launch_sparse_inst<BNV, false, true, E, true>(map_s, map_d, p, grid, stream)
+#define BM_SPR(BNV, E, R_) if (bn == BNV && tile_rows == R_) return launch_sparse_inst<BNV, false, true, E, true, R_>(map_s, map_d, p, grid, stream)
+        if (epi == EPI_I32) {
+            BM_SPR(64, EPI_I32, 32); BM_SPR(64, EPI_I32, 64); BM_SPR(32, EPI_I32, 32); BM_SPR(32, EPI_I32, 64);
+            BM_SPR(16, EPI_I32, 32); BM_SPR(16, EPI_I32, 64);
+        } else if (epi == EPI_F16_ROWCOL) {
+            BM_SPR(64, EPI_F16_ROWCOL, 32); BM_SPR(64, EPI_F16_ROWCOL, 64); BM_SPR(32, EPI_F16_ROWCOL, 32);
+            BM_SPR(32, EPI_F16_ROWCOL, 64); BM_SPR(16, EPI_F16_ROWCOL, 32); BM_SPR(16, EPI_F16_ROWCOL, 64);
+        }
+#undef BM_SPR
         if (epi == EPI_I32) {
             if (bn == 256) BM_SPP(256, EPI_I32); if (bn == 128) BM_SPP(128, EPI_I32); if (bn == 64) BM_SPP(64, EPI_I32);
             if (bn == 32) BM_SPP(32, EPI_I32);   if (bn == 16) BM_SPP(16, EPI_I32);

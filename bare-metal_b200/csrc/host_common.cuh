@@ -52,6 +52,7 @@ enum : int {
     OPT_TAIL_NARROW,         // 0 switches the half-height tiles of a partly filled last wave off
     OPT_PDL,                 // 0 launches without programmatic stream serialization
     OPT_GATHER_GBS,          // fused all-gather: GB/s of peer stores a GPU may send (0 = unpaced)
+    OPT_DECODE_TILE_ROWS,    // row-balanced decode tiles: rows per ring stage (0 automatic; 32 / 64 / 128 pins it)
     OPT_COUNT
 };
 struct OptionSpec { const char* name; const char* env; int def; };
@@ -62,6 +63,7 @@ inline const OptionSpec* option_specs() {
         {"tma_store", "BM_TMA_STORE", 1},         {"dense_group_m", "BM_DENSE_GROUP_M", -1},
         {"sparse_col_first", "BM_SPARSE_COL_FIRST", -1}, {"tail_narrow", "BM_TAIL_NARROW", 1},
         {"pdl", "BM_PDL", 1},                     {"gather_gbs", "BM_GATHER_GBS", 680},
+        {"decode_tile_rows", "BM_DECODE_TILE_ROWS", 0},
     };
     return specs;
 }

@@ -35,17 +35,22 @@ constexpr int kSpMetaBytes = 4096;               // metadata bytes per (128-row 
 constexpr int kSpSmemBudget = 216 * 1024;         // one CTA per SM
 constexpr int kSpSmemBudgetNarrow = 100 * 1024;   // narrow token tiles (decode): two CTAs per SM
 
-template <int BN>
+// ROWS < 128 (packed weights, row-balanced decode tiles only): a stage holds at most ROWS rows of the sparse
+// operand, so the ring is deeper — a CTA that was dealt a few dozen rows (a slab of an N-split layer) walks its
+// K blocks with up to 12 of them in flight instead of 4.  The MMA still spans 128 lanes; what it reads beyond the
+// stage's rows (the following stages' bytes) lands in accumulator lanes nobody stores.
+template <int BN, int ROWS = kBM>
 struct SparseCfg {
-    static constexpr int A_BYTES = kBM * 128;                     // 16 KiB compressed
+    static constexpr int A_BYTES = ROWS * 128;                    // compressed values (16 KiB for 128 rows)
     static constexpr int B_BYTES = BN * kSpKLogical;              // dense operand
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + kSpMetaBytes;
+    static constexpr int E_BYTES = ROWS * 32;                     // metadata (kSpMetaBytes for 128 rows)
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + E_BYTES;
     // Decode-shaped tiles (BN <= 64) take half an SM each: two CTAs per SM keep twice as many
     // independent streams in flight and let the CTAs of the next launch settle in while the last
     // ones of this launch drain.
     static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
     static constexpr int STAGES_RAW = (BN <= 32 ? kSpSmemBudgetNarrow : BN == 64 ? 108 * 1024 : kSpSmemBudget) / STAGE_BYTES;
-    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int STAGES = STAGES_RAW > (ROWS < kBM ? 12 : 8) ? (ROWS < kBM ? 12 : 8) : STAGES_RAW;
     static constexpr int E_COLS = STAGES * 8;                     // 2 x tcgen05.cp of 4 columns per stage
     static constexpr int ACC_BUFS = (2 * BN + E_COLS <= 512) ? 2 : 1;
     static constexpr int E_BASE = ACC_BUFS * BN;
@@ -59,6 +64,7 @@ struct SparseCfg {
     static constexpr int STRIP_OFFSET = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16;
     static constexpr int SMEM_BYTES = STRIP_OFFSET + EPI_WARPS * (int)sizeof(EpiStrip<NC>) + 1024;
     static_assert(STAGES >= 2, "tile too large for the shared-memory ring");
+    static_assert(ROWS == kBM || (ROWS % 8 == 0 && STAGES * B_BYTES >= kBM * 128), "short stages: over-read must stay inside the ring");
     static_assert(COLS_NEEDED <= 512, "tensor memory over-subscribed");
 };
 
@@ -97,8 +103,10 @@ struct WorkIter {
     int tile, tiles, step, tiles_r;
     int row, row_end;                  // row-balanced mode
     bool row_balanced;
-    __device__ WorkIter(const SparseParams& p, int cta, int ctas, int tiles_)
-        : tile(cta), tiles(tiles_), step(ctas), tiles_r(p.tiles_r), row_balanced(p.row_balanced != 0) {
+    int tile_rows;                     // rows per tile in row-balanced mode (128, or the kernel's shorter stage)
+    __device__ WorkIter(const SparseParams& p, int cta, int ctas, int tiles_, int tile_rows_ = 128)
+        : tile(cta), tiles(tiles_), step(ctas), tiles_r(p.tiles_r), row_balanced(p.row_balanced != 0),
+          tile_rows(tile_rows_) {
         const long long r8 = (p.sparse_rows + 7) / 8;
         row = static_cast<int>(r8 * cta / ctas) * 8;
         row_end = static_cast<int>(r8 * (cta + 1) / ctas) * 8;
@@ -108,7 +116,7 @@ struct WorkIter {
             if (row >= row_end) return false;
             s.tile = 0;
             s.row0 = row;
-            s.nrows = row_end - row < 128 ? row_end - row : 128;
+            s.nrows = row_end - row < tile_rows ? row_end - row : tile_rows;
             row += s.nrows;
             return true;
         }
@@ -129,11 +137,12 @@ struct WorkIter {
 // tcgen05.mma.sp.kind::f16 with fp32 accumulators, whose bits the EPI_I32 epilogue stores as they
 // are.  BN counts fp16 elements; the tensor maps are byte maps (inner extents doubled).  Only the
 // reference orientation is built: DENSE_MN, not TRANSPOSED, not PACKED.
-template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false, bool F16 = false>
-__global__ void __launch_bounds__(SparseCfg<BN>::THREADS, SparseCfg<BN>::CTAS_PER_SM)
+template <int BN, bool DENSE_MN, bool TRANSPOSED, int EPI, bool PACKED = false, bool F16 = false, int ROWS = kBM>
+__global__ void __launch_bounds__(SparseCfg<BN, ROWS>::THREADS, SparseCfg<BN, ROWS>::CTAS_PER_SM)
 igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_d,
                     const SparseParams p) {
-    using Cfg = SparseCfg<BN>;
+    using Cfg = SparseCfg<BN, ROWS>;
+    static_assert(ROWS == kBM || (PACKED && TRANSPOSED), "short stages are for row-balanced tiles of packed weights");
     static_assert(!DENSE_MN || BN % 128 == 0, "MN-major dense operand is loaded in 128-column boxes");
     static_assert(!F16 || (DENSE_MN && !TRANSPOSED && !PACKED && EPI == EPI_I32), "fp16: reference orientation only");
     constexpr bool ROTATE_K = TRANSPOSED && BN <= 64;         // decode shapes: per-CTA starting K block (see the producer)
@@ -143,9 +152,12 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const uint32_t a_smem0 = smem_base;
+    // ring order: values, dense operand, metadata — with short stages metadata first, so that what the 128-lane
+    // MMA and metadata copy read beyond a short stage is always ring memory (values, then the dense operand)
+    const uint32_t e_short0 = smem_base;
+    const uint32_t a_smem0 = ROWS == kBM ? smem_base : e_short0 + Cfg::STAGES * Cfg::E_BYTES;
     const uint32_t b_smem0 = a_smem0 + Cfg::STAGES * Cfg::A_BYTES;
-    const uint32_t e_smem0 = b_smem0 + Cfg::STAGES * Cfg::B_BYTES;
+    const uint32_t e_smem0 = ROWS == kBM ? b_smem0 + Cfg::STAGES * Cfg::B_BYTES : e_short0;
     const uint32_t bar0 = smem_base + Cfg::BAR_OFFSET;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (Cfg::STAGES + s); };
@@ -192,7 +204,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             prefetch_tensormap(&map_d);
             uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
             bool ok = true;
-            WorkIter work(p, blockIdx.x, gridDim.x, num_tiles);
+            WorkIter work(p, blockIdx.x, gridDim.x, num_tiles, ROWS);
             WorkSegment seg;
             while (ok && work.next(seg)) {
                 const int r0 = seg.row0;
@@ -218,7 +230,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                         mbar_expect_tx(bar, static_cast<uint32_t>(seg.nrows) * kSpPackedRowBytes + Cfg::B_BYTES);
                         const uint8_t* slice = p.meta_tiled + static_cast<size_t>(kb) * rows_padded * kSpPackedRowBytes;
                         bulk_load(a_smem0 + stage * Cfg::A_BYTES, slice + static_cast<size_t>(r0) * 128, seg.nrows * 128, bar);
-                        bulk_load(e_smem0 + stage * kSpMetaBytes, slice + rows_padded * 128 + static_cast<size_t>(r0) * 32,
+                        bulk_load(e_smem0 + stage * Cfg::E_BYTES, slice + rows_padded * 128 + static_cast<size_t>(r0) * 32,
                                   seg.nrows * 32, bar);
                     } else {
                         mbar_expect_tx(bar, Cfg::A_BYTES + Cfg::B_BYTES + kMetaStage);
@@ -240,7 +252,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                             tma_load_2d(b_addr + j * (BN * 128), &map_d, bar, kb * kSpKLogical + j * 128, c0);
                     }
                     if constexpr (!PACKED)
-                        bulk_load(e_smem0 + stage * kSpMetaBytes, meta_row + static_cast<size_t>(kb) * kMetaStage,
+                        bulk_load(e_smem0 + stage * Cfg::E_BYTES, meta_row + static_cast<size_t>(kb) * kMetaStage,
                                   kMetaStage, bar);
                     issued |= 1u << stage;
                     issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
@@ -262,7 +274,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
             constexpr uint32_t idesc = F16 ? make_idesc_f16(kBM, BN, DENSE_MN, true) : make_idesc_i8(kBM, BN, DENSE_MN, true);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            WorkIter work(p, blockIdx.x, gridDim.x, num_tiles);
+            WorkIter work(p, blockIdx.x, gridDim.x, num_tiles, ROWS);
             WorkSegment seg;
             while (ok && work.next(seg)) {
                 if (!bounded_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
@@ -277,7 +289,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
                     tc_fence_after_sync();
                     const uint32_t a_addr = a_smem0 + stage * Cfg::A_BYTES;
                     const uint32_t b_addr = b_smem0 + stage * Cfg::B_BYTES;
-                    const uint32_t e_addr = e_smem0 + stage * kSpMetaBytes;
+                    const uint32_t e_addr = e_smem0 + stage * Cfg::E_BYTES;
                     const uint32_t e_tmem = tmem_base + Cfg::E_BASE + stage * 8;
                     // metadata: rows are 16 B apart, 8-row groups 128 B apart, no swizzle
 #pragma unroll
@@ -326,7 +338,7 @@ igemm_sparse_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_cons
         const int half = (warp - 2) >> 2;                     // 0 unless the tile is drained by 8 warps
         EpiStrip<Cfg::NC>* strip = reinterpret_cast<EpiStrip<Cfg::NC>*>(smem_gen + Cfg::STRIP_OFFSET) + (warp - 2);
         uint32_t acc = 0, acc_phase = 0;
-        WorkIter work(p, blockIdx.x, gridDim.x, num_tiles);
+        WorkIter work(p, blockIdx.x, gridDim.x, num_tiles, ROWS);
         WorkSegment seg;
         while (work.next(seg)) {
             const int r0 = seg.row0;

@@ -251,7 +251,10 @@ int bm_last_device_status(int *code);
 /* Launcher options (tuning / testing switches; no reference counterpart — the reference fixes
  * launch geometry in its bench drivers, bench.cu:375-636).  Names: "force_bn" (pin the tile width;
  * 0 = choose), "dense_pair", "sparse_pair" (0 = single-CTA kernels only), "row_balanced"
- * (0 = whole 128-row tiles on the decode shapes), "tma_store" (0 = direct-store epilogue), "dense_group_m", "sparse_col_first" (-1 automatic), "tail_narrow", "pdl", "gather_gbs".
+ * (0 = whole 128-row tiles on the decode shapes), "tma_store" (0 = direct-store epilogue),
+ * "dense_group_m", "sparse_col_first" (-1 automatic), "tail_narrow", "pdl", "gather_gbs",
+ * "decode_tile_rows" (row-balanced decode tiles on packed weights: 0 = choose the ring-stage height
+ * from the rows a CTA is dealt, 32 / 64 / 128 pins it).
  * Each starts from the environment variable BM_<NAME> read once at first use, else its default;
  * launchers never read the environment on the launch path.  Process-wide; set them while no
  * other thread is launching.  Unknown names return BM_ERR_LAYOUT. */

@@ -88,7 +88,7 @@ def test_launcher_options_are_set_and_read_without_a_device():
     L = _lib.load()
     for name, default in (("force_bn", 0), ("dense_pair", 1), ("sparse_pair", 1), ("row_balanced", 1),
                           ("tma_store", 1), ("dense_group_m", -1), ("sparse_col_first", -1), ("tail_narrow", 1),
-                          ("pdl", 1), ("gather_gbs", 680)):
+                          ("pdl", 1), ("gather_gbs", 680), ("decode_tile_rows", 0)):
         if ("BM_" + name.upper()) not in os.environ:
             assert _lib.get_option(name) == default, name
     _lib.set_option("force_bn", 128)

@@ -274,3 +274,28 @@ def test_pair_kernel_tile_orders_give_the_same_integers(order):
         ig.w8a8_sparse_i32(T(X), T(comp), tiled, C, M, N, K)
     assert_clean_status()
     assert np.array_equal(C.cpu().numpy(), oracle.igemm_nt(X, oracle.decompress_rows(comp, nib)))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2400, 1024), (16, 3584, 512), (64, 4744, 768), (33, 9480, 512)])
+def test_short_stage_decode_tiles(M, N, K):
+    """A CTA that is dealt few rows (the slab of an N-split layer) uses ring stages of 32 or 64 rows and a deeper
+    ring; whatever the stage height, chosen or pinned, the integers and the fp16 outputs are the oracle's."""
+    from _gpu import options
+    comp, nib = oracle.gen_sparse_rows(N, K, 6, 71)
+    X = oracle.gen_int8((M, K), 6, 72)
+    want = oracle.igemm_nt(X, oracle.decompress_rows(comp, nib))
+    packed = ig.sp_pack_weights(T(comp), T(nib), ig.BM_META_ROWS, N, K)
+    sa, sw = oracle.gen_scales(M, 6, 3), oracle.gen_scales(N, 6, 4)
+    want16 = oracle.dequant_w8a8_f16(want, sa, sw).view(np.uint16)
+    for rows in (0, 32, 64, 128):
+        with options(decode_tile_rows=rows):
+            guard = torch.full((M + 2, N), 0x5A5A5A5A, dtype=torch.int32, device=dev())
+            ig.w8a8_sparse_i32_packed(T(X), packed, guard[1:M + 1], M, N, K)
+            assert_clean_status()
+            g = guard.cpu().numpy()
+            assert np.array_equal(g[1:M + 1], want), f"stage rows {rows}"
+            assert (g[0] == 0x5A5A5A5A).all() and (g[-1] == 0x5A5A5A5A).all()
+            D = torch.zeros((M, N), dtype=torch.float16, device=dev())
+            ig.w8a8_sparse_linear_packed(T(X), packed, D, T(sa), T(sw), M, N, K)
+            assert_clean_status()
+            assert ulp_diff_f16(D.cpu().numpy().view(np.uint16), want16) <= 1, f"stage rows {rows}"
