@@ -58,8 +58,8 @@ struct SparseCfg {
     static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
                                    : COLS_NEEDED <= 256 ? 256 : 512;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int EPI_WARPS = BN >= 128 ? 8 : 4;           // two per lane quarter for wide tiles
-    static constexpr int NC = BN >= 128 ? BN / 2 : (BN == 64 ? 64 : 32);   // accumulator columns drained per warp
+    static constexpr int EPI_WARPS = BN >= 64 ? 8 : 4;            // two per lane quarter from 64 columns up
+    static constexpr int NC = BN >= 64 ? BN / 2 : 32;             // accumulator columns drained per warp
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int STRIP_OFFSET = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16;
     static constexpr int SMEM_BYTES = STRIP_OFFSET + EPI_WARPS * (int)sizeof(EpiStrip<NC>) + 1024;
