@@ -141,14 +141,18 @@ __device__ __forceinline__ void emit_col_chunk(const EpilogueParams& p, int col,
                                                const uint32_t (&r)[32], const float* s_scale, float lane_s) {
     using T = typename OutType<EPI>::type;
     if (col >= p.cols) return;
-    T* dst = reinterpret_cast<T*>(p.out) + col;
+    T* dst = reinterpret_cast<T*>(p.out) + col + static_cast<long long>(row0) * p.ld;
+    // all conversions first (independent, so they overlap), then the stores: with both in one loop every store
+    // waited for its own scale load and conversions
+    T v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+        v[k] = convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s, epi_rowcol(EPI) ? s_scale[k] : 0.f, 0);
+    const int live = row_limit - row0;            // rows of this chunk inside the output
 #pragma unroll
     for (int k = 0; k < 32; ++k) {
-        const int row = row0 + k;
-        if (row < row_limit)
-            dst[static_cast<long long>(row) * p.ld] =
-                convert_acc<EPI>(static_cast<int32_t>(r[k]), p.tensor_scale, lane_s,
-                                 epi_rowcol(EPI) ? s_scale[k] : 0.f, 0);
+        if (k < live) *dst = v[k];
+        dst += p.ld;
     }
 }
 
