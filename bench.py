@@ -314,8 +314,8 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the sparse / decode / layer-chain side measurements")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: fused = GEMM epilogue stores to all ranks over NVLink; nccl = GEMM then all-gather")
-    ap.add_argument("--lanes", type=int, default=2, choices=[1, 2],
-                    help="N > 1, fused gather: steps in flight (2 = consecutive steps alternate between two streams)")
+    ap.add_argument("--lanes", type=int, default=2, choices=[1, 2, 3, 4],
+                    help="N > 1, fused gather: steps in flight (L > 1: consecutive steps take turns on L streams)")
     ap.add_argument("--workload", default="dense", choices=["dense", "sparse", "decode", "online_quant", "hgemm_sparse"],
                     help="with --profile: which kernel to run (dense = the headline; sparse = 2:4 at 4096^3; "
                          "decode = the skinny sparse GEMM)")
@@ -378,8 +378,8 @@ def main() -> None:
         # two steps in flight: consecutive steps are independent problems (rotating operand sets, the layer's two
         # output buffers), so they alternate between two streams — the GEMM of one step overlaps the NVLink tail
         # and the group barrier of the other, as a server does with independent micro-batches
-        if args.gather == "fused" and args.lanes == 2:
-            lanes = [torch.cuda.Stream(), torch.cuda.Stream()]
+        if args.gather == "fused" and args.lanes > 1:
+            lanes = [torch.cuda.Stream() for _ in range(args.lanes)]
 
     def step(i: int):
         s = i % n_sets
@@ -388,7 +388,7 @@ def main() -> None:
             return D_d[s]
         layer.W = W_d[s]
         if lanes is not None:
-            return layer.forward_fused(A_d[s], sa_d, lane=i & 1, stream=lanes[i & 1])
+            return layer.forward_fused(A_d[s], sa_d, lane=i % len(lanes), stream=lanes[i % len(lanes)])
         if args.gather == "fused":
             return layer.forward_fused(A_d[s], sa_d)
         return layer.forward_nccl(A_d[s], sa_d, out=G_blocks, local=D_d[s])
@@ -514,8 +514,8 @@ def main() -> None:
         else:
             par = f"n-split x{world} ({n_len} of {N_TOTAL} weight columns per GPU)" + (
                 " + all-gather of the fp16 output fused into the GEMM epilogue (paced peer TMA stores) + group barrier"
-                + ("; two steps in flight (independent steps alternate between two streams, two output buffers)"
-                   if lanes is not None else "")
+                + (f"; {len(lanes)} steps in flight (independent steps take turns on {len(lanes)} streams, each with its own "
+                   "output buffers and barrier instance)" if lanes is not None else "")
                 if args.gather == "fused" else " + NCCL all-gather of the fp16 output")
             launches = args.steps * (2 if args.gather == "fused" else 1)     # per rank: GEMM+gather kernel, barrier kernel
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
