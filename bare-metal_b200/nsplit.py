@@ -126,7 +126,6 @@ class _Sharded:
         self.mode = mode
         self._sym = {}
         self._turn = {}
-        self._lane_done = {}          # forward_push: event behind the last barrier of each lane
         lens = [None] * self.world
         dist.all_gather_object(lens, (self.n0, self.n_len), group=self.group)
         self.slabs = lens
@@ -222,45 +221,6 @@ class ColumnShardedLinear(_Sharded):
         _lib.check(rc, "bm_w8a8_f16_gather")
         if barrier:     # every rank's stores are complete before anyone reads
             GroupBarrier.of(self.group, X.device, lane or 0)(stream)
-        return buf
-
-    # ---- GEMM, then a copy kernel pushes the slab (pipelined over steps) -----------------------
-    def forward_push(self, X, sa, lane=None, stream=None, push_stream=None, barrier_stream=None):
-        """The slab GEMM writes into this rank's own [M x N] output, the copy kernel (bm_gather_slab_f16, paced
-        peer stores) sends the slab to the peers, then the barrier.  With `push_stream` / `barrier_stream` the three
-        run on streams of their own, ordered by events, so that over a sequence of independent steps the GEMM of
-        step i + 1 runs while step i's slab crosses NVLink and the copies of consecutive steps follow one another on
-        the link.  For shapes whose transfer takes longer than their GEMM this beats the fused kernel: a slab of one
-        or two waves of tiles has nothing to send until its GEMM is over, and a fused kernel keeps its SMs while
-        its stores wait for link tokens.  The call first orders `stream` behind the previous barrier of `lane`
-        (the step that last used this lane's buffers)."""
-        from . import _lib
-        M = X.shape[0]
-        lane_key = lane or 0
-        buf, _, slab_ptrs = self._symmetric(M, X.device, lane)
-        s_gemm = stream if stream is not None else torch.cuda.current_stream()
-        s_push = push_stream if push_stream is not None else s_gemm
-        s_bar = barrier_stream if barrier_stream is not None else s_push
-        done = self._lane_done.get(lane_key)
-        if done is not None:
-            s_gemm.wait_event(done)
-        with torch.cuda.stream(s_gemm):
-            self._local(X, sa, buf[:, self.n0:self.n0 + self.n_len], self.n_total)
-        if s_push is not s_gemm:
-            ev = torch.cuda.Event()
-            ev.record(s_gemm)
-            s_push.wait_event(ev)
-        rc = _lib.load().bm_gather_slab_f16(slab_ptrs, self.world, self.rank, M, self.n_len, self.n_total,
-                                            s_push.cuda_stream)
-        _lib.check(rc, "bm_gather_slab_f16")
-        if s_bar is not s_push:
-            ev = torch.cuda.Event()
-            ev.record(s_push)
-            s_bar.wait_event(ev)
-        GroupBarrier.of(self.group, X.device, 0)(s_bar)      # one instance: the barriers of all steps are in stream order
-        done = torch.cuda.Event()
-        done.record(s_bar)
-        self._lane_done[lane_key] = done
         return buf
 
     def forward(self, X, sa):

@@ -312,9 +312,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the sparse / decode / layer-chain side measurements")
-    ap.add_argument("--gather", default="fused", choices=["fused", "push", "nccl"],
-                    help="N > 1: fused = GEMM epilogue stores to all ranks over NVLink; push = GEMM, then a copy kernel "
-                         "sends the slab, the steps pipelined over three streams; nccl = GEMM then all-gather")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: fused = GEMM epilogue stores to all ranks over NVLink; nccl = GEMM then all-gather")
     ap.add_argument("--lanes", type=int, default=2, choices=[1, 2, 3, 4],
                     help="N > 1, fused gather: steps in flight (L > 1: consecutive steps take turns on L streams)")
     ap.add_argument("--workload", default="dense", choices=["dense", "sparse", "decode", "online_quant", "hgemm_sparse"],
@@ -374,17 +373,13 @@ def main() -> None:
     layer = G_blocks = None
     lanes = None
     if world > 1:
-        layer = nsplit.ColumnShardedLinear(W_d[0], sw_d, N_TOTAL, n0, mode="nccl" if args.gather == "nccl" else "fused")
+        layer = nsplit.ColumnShardedLinear(W_d[0], sw_d, N_TOTAL, n0, mode=args.gather)
         G_blocks = torch.empty((world, M, n_len), dtype=torch.float16, device=devn)
         # two steps in flight: consecutive steps are independent problems (rotating operand sets, the layer's two
         # output buffers), so they alternate between two streams — the GEMM of one step overlaps the NVLink tail
         # and the group barrier of the other, as a server does with independent micro-batches
         if args.gather == "fused" and args.lanes > 1:
             lanes = [torch.cuda.Stream() for _ in range(args.lanes)]
-        # push: one stream for the GEMMs, one for the copy kernels (so the slabs of consecutive steps follow one
-        # another on the link), one for the barriers; `--lanes` steps in flight (a lane = a pair of output buffers)
-        if args.gather == "push":
-            lanes = [torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()]
 
     def step(i: int):
         s = i % n_sets
@@ -392,9 +387,6 @@ def main() -> None:
             ig.w8a8_linear(A_d[s], W_d[s], D_d[s], sa_d, sw_d, M, n_len, K)
             return D_d[s]
         layer.W = W_d[s]
-        if args.gather == "push":
-            return layer.forward_push(A_d[s], sa_d, lane=i % max(2, args.lanes), stream=lanes[0], push_stream=lanes[1],
-                                      barrier_stream=lanes[2])
         if lanes is not None:
             return layer.forward_fused(A_d[s], sa_d, lane=i % len(lanes), stream=lanes[i % len(lanes)])
         if args.gather == "fused":
@@ -420,7 +412,7 @@ def main() -> None:
     want_full = oracle.dequant_w8a8_f16(oracle.igemm_nt(np.ascontiguousarray(A_h[rows]), W_full_h), sa_h[rows], sw_full_h)
     out0 = step(0)
     cx.sync()
-    if world == 1 or args.gather in ("fused", "push"):
+    if world == 1 or args.gather == "fused":
         got = out0.cpu().numpy()[rows]            # N > 1: the whole row, i.e. every peer's slab as it arrived here
     else:
         got = nsplit.ColumnShardedLinear.blocks_to_row_major(out0).cpu().numpy()[rows]
@@ -524,11 +516,8 @@ def main() -> None:
                 " + all-gather of the fp16 output fused into the GEMM epilogue (paced peer TMA stores) + group barrier"
                 + (f"; {len(lanes)} steps in flight (independent steps take turns on {len(lanes)} streams, each with its own "
                    "output buffers and barrier instance)" if lanes is not None else "")
-                if args.gather == "fused" else
-                " + copy kernel that stores the slab to the peers (paced) + group barrier; GEMM, copies and barriers of "
-                f"consecutive independent steps on three streams, {max(2, args.lanes)} steps in flight"
-                if args.gather == "push" else " + NCCL all-gather of the fp16 output")
-            launches = args.steps * {"fused": 2, "push": 3}.get(args.gather, 1)   # per rank: GEMM(+gather), [copy,] barrier
+                if args.gather == "fused" else " + NCCL all-gather of the fp16 output")
+            launches = args.steps * (2 if args.gather == "fused" else 1)     # per rank: GEMM+gather kernel, barrier kernel
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong" if world > 1 else "weak",
@@ -637,7 +626,7 @@ def sharded_headline_detail(cx, nsplit, _lib, layer, step, gemm_only, A_d, W_d, 
     target = max(kern_ms, t_link)
     return {"single_gpu_ms": single_ms, "gemm_only_ms": kern_ms, "gemm_only_efficiency": single_ms / (cx.world * kern_ms),
             "gathered_ms": ms_step, "gathered_efficiency": single_ms / (cx.world * ms_step),
-            "steps_in_flight": args.lanes if args.gather == "fused" else (max(2, args.lanes) if args.gather == "push" else 1),
+            "steps_in_flight": args.lanes if args.gather == "fused" else 1,
             "single_step_latency_ms": t_serial,
             "fused_kernel_without_barrier_ms": t_kernel, "nccl_all_gather_ms": t_nccl,
             "fused_collective": {"bound": "nvlink receive" if t_link > kern_ms else "tensor",
