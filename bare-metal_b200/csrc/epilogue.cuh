@@ -225,29 +225,6 @@ struct StorePace {
 __device__ __forceinline__ unsigned long long pace_now() {
     return (global_timer_ns() & 0x00FFFFFFFFFFFFFFull) << 4;
 }
-// Reserves n consecutive remote stores (n tokens of the GPU's bucket) with one round of atomics and returns the
-// virtual time of the first; the caller issues store i once pace_now() has reached the returned time + i * cost
-// (pace_until).  One reservation per warp and tile: with a round of atomics per store, the microsecond each round
-// takes sat on the epilogue's critical path as soon as a box went to several peers.
-__device__ __forceinline__ unsigned long long pace_reserve(const StorePace& pace, int n) {
-    constexpr unsigned long long kCredit = 16ull * 1000;            // 1 us
-    const unsigned long long units = static_cast<unsigned long long>(n) * pace.cost;
-    const unsigned long long now = pace_now();
-    atomicMax(pace.clock, now > kCredit ? now - kCredit : 0ull);
-    unsigned long long token = atomicAdd(pace.clock, units);
-    if (token > now + 16ull * 1000000000) {                          // a clock from another epoch: restart it
-        atomicExch(pace.clock, now);
-        token = now;
-    }
-    return token;
-}
-__device__ __forceinline__ void pace_until(unsigned long long slot) {
-    constexpr unsigned long long kGiveUp = 16ull * 2000000;         // 2 ms
-    unsigned long long now = pace_now();
-    const unsigned long long t0 = now;
-    while (now < slot && now - t0 < kGiveUp) now = pace_now();
-}
-
 __device__ __forceinline__ void pace_remote_store(unsigned long long* clock, unsigned cost) {
     constexpr unsigned long long kCredit = 16ull * 1000;            // 1 us
     constexpr unsigned long long kGiveUp = 16ull * 2000000;         // 2 ms
@@ -276,7 +253,7 @@ template <int EPI, int NC, int NBUF, class Source>
 __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const CUtensorMap* maps, int n_maps, const Source& src,
                                                int row0, int lane, int col0, const EpiStrip<NC>* strip, float lane_s,
                                                uint32_t stage_smem0, uint32_t& box_count, int col_limit,
-                                               const StorePace& pace = StorePace{}) {
+                                               const StorePace& pace = StorePace{nullptr, 0u, 0u, 0}) {
     using T = typename OutType<EPI>::type;
     static_assert(NC % 32 == 0, "drained in chunks of 32 columns");
     constexpr int CHUNKS = NC / 32;
@@ -289,13 +266,6 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const CU
 
     uint32_t rr[2][32];
     if (col0 < col_limit) src.issue(0, rr[0]);
-    // lane 0: virtual time of this call's next remote store (all of the call's remote stores reserved at once)
-    unsigned long long pace_slot = 0;
-    if (pace.cost != 0 && lane == 0 && col0 < col_limit) {
-        const int live_cols = col_limit - col0 < NC ? col_limit - col0 : NC;
-        const int remote = __popc(pace.remote_mask & ((1u << n_maps) - 1u));
-        if (remote > 0) pace_slot = pace_reserve(pace, ((live_cols + COLS_PER_BOX - 1) / COLS_PER_BOX) * remote);
-    }
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
         const int cur = c & 1;
@@ -339,10 +309,7 @@ __device__ __forceinline__ void drain_tma_from(const EpilogueParams& p, const CU
                 for (int i = 0; i < n_maps; ++i) {
                     int d = pace.first + i;
                     if (d >= n_maps) d -= n_maps;
-                    if (pace.cost != 0 && ((pace.remote_mask >> d) & 1u)) {
-                        pace_until(pace_slot);
-                        pace_slot += pace.cost;
-                    }
+                    if (pace.cost != 0 && ((pace.remote_mask >> d) & 1u)) pace_remote_store(pace.clock, pace.cost);
                     tma_store_2d(maps + d, stage_smem, box_c0, row0);
                 }
                 bulk_commit_group();
@@ -357,7 +324,7 @@ __device__ __forceinline__ void drain_accumulator_tma(const EpilogueParams& p, c
                                                       uint32_t taddr, int row0, int lane, int col0,
                                                       const EpiStrip<NC>* strip, float lane_s, uint32_t stage_smem0,
                                                       uint32_t& box_count, int col_limit,
-                                                      const StorePace& pace = StorePace{}) {
+                                                      const StorePace& pace = StorePace{nullptr, 0u, 0u, 0}) {
     drain_tma_from<EPI, NC, NBUF>(p, maps, n_maps, TmemSource{taddr}, row0, lane, col0, strip, lane_s, stage_smem0,
                                   box_count, col_limit, pace);
 }
